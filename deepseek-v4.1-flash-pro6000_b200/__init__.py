@@ -1,0 +1,167 @@
+"""Host-side mirror of the decode-tail call surface on top of the C-ABI library (libds41_b200.so).
+
+The functions follow the reference engine's sampler interface (engine/include/ds41/engine.hpp:181-227):
+`Rng`, `AttemptCounter`, `Purpose`, `sample`, `argmax`, `reject_sample` -- but they take LOGITS on the device and
+return decisions, because the fused device path never materialises FP64 probability rows.  Torch is used only as
+the owner of device memory and streams; every computation happens inside the library's CUDA kernels.  There is no
+CPU fallback: without the built library or without a CUDA device every call raises.
+"""
+import ctypes as C
+import enum
+import os
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libds41_b200.so")
+MAX_VOCAB = 131072
+MAX_HISTORY = 65535
+
+_u64, _u32, _i32, _i64, _f64, _f32, _P = C.c_uint64, C.c_uint32, C.c_int32, C.c_int64, C.c_double, C.c_float, C.c_void_p
+
+
+class Purpose(enum.IntEnum):
+    """engine.hpp:187-192 / spark.h:96"""
+    Target = 0
+    Draft = 1
+    Accept = 2
+    Residual = 3
+
+
+class SparkResult(C.Structure):
+    """ds41_spark_result, spark.h:106-108"""
+    _fields_ = [("tokens", _i32 * 6), ("emitted", C.c_int), ("accepted_drafts", C.c_int),
+                ("accepted_input_rows", C.c_int), ("rejected", C.c_int)]
+
+
+RESULT_DTYPE = np.dtype([("tokens", np.int32, 6), ("emitted", np.int32), ("accepted_drafts", np.int32),
+                         ("accepted_input_rows", np.int32), ("rejected", np.int32)])
+
+
+class SampleArgs(C.Structure):
+    _fields_ = [("struct_bytes", _u32), ("rows", _i32), ("vocab", _i32), ("logits", _P), ("logits_stride", _i64),
+                ("temperature", _f64), ("top_p", _f64), ("top_k", _i32), ("repetition", _f32), ("presence", _f32),
+                ("frequency", _f32), ("history", _P), ("history_stride", _i64), ("history_len", _P), ("mask", _P),
+                ("mask_stride", _i64), ("seeds", _P), ("steps", _P), ("slot", _u32), ("purpose", _u32),
+                ("tokens", _P), ("status", _P)]
+
+
+class VerifyArgs(C.Structure):
+    _fields_ = [("struct_bytes", _u32), ("sequences", _i32), ("drafts", _i32), ("vocab", _i32),
+                ("target_logits", _P), ("draft_logits", _P), ("draft_ids", _P), ("temperature", _f64),
+                ("top_p", _f64), ("seeds", _P), ("steps", _P), ("results", _P), ("status", _P), ("scratch", _P),
+                ("scratch_bytes", C.c_size_t)]
+
+
+_lib = None
+
+
+def lib():
+    """Loads the CUDA library; raises if it has not been built (no fallback path exists)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: run `python __graft_entry__.py` (build) first")
+        L = C.CDLL(LIB_PATH)
+        L.ds41_spark_error.restype = C.c_char_p
+        L.ds41_spark_rng_word_v2.restype = _u32
+        L.ds41_spark_rng_word_v2.argtypes = [_u64, _u64, _u32, _u32, _u64]
+        L.ds41_spark_uniform_v2.restype = _f64
+        L.ds41_spark_uniform_v2.argtypes = [_u64, _u64, _u32, _u32, _u64]
+        L.ds41_b200_sample_logits.argtypes = [C.POINTER(SampleArgs), _P]
+        _lib = L
+    return _lib
+
+
+def last_error():
+    return lib().ds41_spark_error().decode()
+
+
+def _check(rc, what):
+    if rc:
+        raise RuntimeError(f"{what}: cudaError {rc} ({last_error()})")
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dev(t, dtype, name):
+    if t is None:
+        return None
+    if not t.is_cuda or t.dtype != dtype or not t.is_contiguous():
+        raise ValueError(f"{name} must be a contiguous CUDA tensor of {dtype}")
+    return t
+
+
+class Rng:
+    """engine.hpp:193-199: Philox4x32-10 keyed by the request seed (spark_rng.h:23-36)."""
+
+    def __init__(self, seed):
+        self.seed = int(seed)
+
+    def word(self, step, slot, purpose, draw=0):
+        if draw // 4 > 0xFFFFFFFF or slot > 5 or int(purpose) > 3:
+            raise OverflowError("Philox draw counter")
+        return lib().ds41_spark_rng_word_v2(self.seed, step, slot, int(purpose), draw)
+
+    def uniform(self, step, slot, purpose, draw=0):
+        if draw > 8589934591 or slot > 5 or int(purpose) > 3:
+            raise OverflowError("Philox draw counter")
+        return lib().ds41_spark_uniform_v2(self.seed, step, slot, int(purpose), draw)
+
+
+class AttemptCounter:
+    """engine/src/sampling.cpp:111-120: one fresh monotone nonce per attempt; exhaustion is an error."""
+
+    def __init__(self, first=0):
+        self._next, self._exhausted = int(first), False
+
+    def take(self):
+        if self._exhausted:
+            raise OverflowError("transaction nonce exhausted")
+        out = self._next
+        if self._next == 2**64 - 1:
+            self._exhausted = True
+        else:
+            self._next += 1
+        return out
+
+
+def sample_logits(logits, temperature, top_p, seeds, steps, slot=0, purpose=Purpose.Target, top_k=0, history=None,
+                  history_len=None, repetition=1.0, presence=0.0, frequency=0.0, mask=None, tokens=None, status=None):
+    """Batched probabilities() + sample() / argmax() on device logits [rows, vocab] (fp32).
+
+    seeds/steps: int64 CUDA tensors holding the uint64 Philox key and attempt counter of each row.
+    Returns (tokens int32 [rows], status int32 [rows]); see ds41_b200.h for the status words."""
+    logits = _dev(logits, torch.float32, "logits") if logits.is_contiguous() else logits
+    if logits.dim() != 2 or logits.stride(1) != 1 or not logits.is_cuda or logits.dtype != torch.float32:
+        raise ValueError("logits must be a CUDA fp32 [rows, vocab] tensor with unit inner stride")
+    rows, vocab = logits.shape
+    seeds = _dev(seeds, torch.int64, "seeds")
+    steps = _dev(steps, torch.int64, "steps")
+    history = _dev(history, torch.int32, "history")
+    history_len = _dev(history_len, torch.int32, "history_len")
+    mask = _dev(mask, torch.int32, "mask")
+    if tokens is None:
+        tokens = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    if status is None:
+        status = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    a = SampleArgs()
+    a.struct_bytes = C.sizeof(SampleArgs)
+    a.rows, a.vocab = rows, vocab
+    a.logits, a.logits_stride = logits.data_ptr(), logits.stride(0)
+    a.temperature, a.top_p, a.top_k = temperature, top_p, top_k
+    a.repetition, a.presence, a.frequency = repetition, presence, frequency
+    a.history = history.data_ptr() if history is not None else None
+    a.history_stride = history.stride(0) if history is not None else 0
+    a.history_len = history_len.data_ptr() if history_len is not None else None
+    a.mask = mask.data_ptr() if mask is not None else None
+    a.mask_stride = mask.stride(0) if mask is not None else 0
+    a.seeds, a.steps = seeds.data_ptr(), steps.data_ptr()
+    a.slot, a.purpose = slot, int(purpose)
+    a.tokens, a.status = tokens.data_ptr(), status.data_ptr()
+    with torch.cuda.device(logits.device):
+        _check(lib().ds41_b200_sample_logits(C.byref(a), _stream()), "ds41_b200_sample_logits")
+    return tokens, status

@@ -1,0 +1,285 @@
+// The per-row kernel: stage -> penalties/mask -> first maximum -> top-k cut -> normaliser (+ top-p cut) -> either
+// the inverse-CDF draw (sampler) or a RowStats record (verifier).  One cluster per row; see row_core.cuh.
+#pragma once
+#include "row_core.cuh"
+
+namespace ds41 {
+
+enum RowMode { kModeSample = 0, kModeStats = 1 };
+
+struct RowArgs {
+  const float *logits;
+  long long logits_stride;
+  int vocab;
+  double temperature;  // already floored; 0 = greedy
+  double top_p;
+  int top_k;
+  float repetition, presence, frequency;
+  const int32_t *history;
+  long long history_stride;
+  const int32_t *history_len;
+  const uint32_t *mask;
+  long long mask_stride;
+  const uint64_t *seeds, *steps;
+  uint32_t slot, purpose;
+  int32_t *tokens;
+  int32_t *status;
+  RowStats *stats;
+};
+
+// Sum of exp over the survivors of `cut` in this warp's region, lanes striding the region in id order; the warp
+// total lands in warp_sum[warp].  Fixed order => the same bits every run.
+template <class Weight>
+__device__ __forceinline__ void region_sums(RowCtx &c, Cut cut, Weight weight) {
+  double acc = 0;
+  for (int it = 0; it < c.region; it += 32) {
+    const int j = c.warp * c.region + it + c.lane;
+    if (j < c.len) {
+      const float y = c.s->y[j];
+      if (survives(y, c.begin + j, cut)) acc += weight(y);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (c.lane == 0) c.s->warp_sum[c.warp] = acc;
+  __syncthreads();
+}
+
+// Inverse CDF in id order over the survivors (reference: draw(), third_party/spark/src/sampling.cpp:18-21).
+// warp_sum[] must hold the region sums.  Returns the token to every thread; *ambiguous is set when the uniform lies
+// within rel_bound * total of a CDF step on either side of the chosen id.
+template <class Weight>
+__device__ int draw_token(RowCtx &c, Cut cut, double u, double rel_bound, Weight weight, int *ambiguous) {
+  RowSmem *s = c.s;
+  double block_total = 0;
+  for (int w = 0; w < kWarps; ++w) block_total += s->warp_sum[w];
+  Slot mine{};
+  mine.d[0] = block_total;
+  const Slot *all = exchange(c, mine);
+  double prefix = 0, total = 0;
+  for (int r = 0; r < c.nranks; ++r) {
+    if (r == c.rank) prefix = total;
+    total += all[r].d[0];
+  }
+  const double target = u * total;
+  const double slack = rel_bound * total;
+  double inner = 0;
+  for (int w = 0; w < c.warp; ++w) inner += s->warp_sum[w];
+  const double start = prefix + inner, end = prefix + (inner + s->warp_sum[c.warp]);
+  int found = -1, amb = 0;
+  if (start <= target && target < end) {  // exactly one warp of the cluster owns the target (intervals tile [0,total))
+    double carry = start;
+    int last_positive = -1;
+    for (int it = 0; it < c.region && found < 0; it += 32) {
+      const int j = c.warp * c.region + it + c.lane;
+      double v = 0;
+      if (j < c.len) {
+        const float y = s->y[j];
+        if (survives(y, c.begin + j, cut)) v = weight(y);
+      }
+      double scan = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const double t = __shfl_up_sync(0xffffffffu, scan, o);
+        if (c.lane >= o) scan += t;
+      }
+      const double cum = carry + scan;
+      const unsigned hit = __ballot_sync(0xffffffffu, v > 0 && target < cum);
+      const unsigned pos = __ballot_sync(0xffffffffu, v > 0);
+      if (hit) {
+        const int l = __ffs(hit) - 1;
+        found = c.begin + c.warp * c.region + it + l;
+        const double cum_l = __shfl_sync(0xffffffffu, cum, l);
+        const double v_l = __shfl_sync(0xffffffffu, v, l);
+        const double below = cum_l - v_l;  // CDF before the chosen id
+        amb = (cum_l - target < slack) || (below > 0 && target - below < slack);
+      } else {
+        if (pos) last_positive = c.begin + c.warp * c.region + it + (31 - __clz(pos));
+        carry = __shfl_sync(0xffffffffu, cum, 31);
+      }
+    }
+    if (found < 0) { found = last_positive; amb = 1; }  // rounding left the target past this region's last step
+    if (c.lane == 0) { s->bcast_i[0] = found; s->bcast_i[1] = amb; s->bcast_i[2] = 1; }
+  }
+  __syncthreads();
+  Slot res{};
+  res.i[0] = -1;
+  if (s->bcast_i[2] == 1) { res.i[0] = s->bcast_i[0]; res.i[1] = s->bcast_i[1]; }  // at most one CTA has an owner
+  __syncthreads();
+  const Slot *got = exchange(c, res);
+  int token = -1;
+  for (int r = 0; r < c.nranks; ++r)
+    if (got[r].i[0] >= 0) { token = got[r].i[0]; amb = got[r].i[1]; }
+  if (token < 0) {
+    // target >= total (only possible by rounding): the reference returns the last id with positive probability
+    int last = -1;
+    for (int it = 0; it < c.region; it += 32) {
+      const int j = c.warp * c.region + it + c.lane;
+      if (j < c.len) {
+        const float y = s->y[j];
+        if (survives(y, c.begin + j, cut) && weight(y) > 0) last = max(last, c.begin + j);
+      }
+    }
+    Slot m2{};
+    m2.i[0] = block_max(c, last);
+    const Slot *g2 = exchange(c, m2);
+    for (int r = 0; r < c.nranks; ++r) token = max(token, g2[r].i[0]);
+    amb = 1;
+  }
+  *ambiguous = amb;
+  return token;
+}
+
+template <int kMode>
+__global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  RowSmem *s = reinterpret_cast<RowSmem *>(smem_raw);
+  RowCtx c = make_ctx(s, a.vocab);
+  const int row = blockIdx.x / c.nranks;
+  const float *logits = a.logits + size_t(row) * a.logits_stride;
+
+  if (c.tid == 0) s->bcast_i[2] = 0;
+  bool used_tma;
+  stage_begin(c, logits, used_tma);
+  if (a.mask) {
+    const uint32_t *mw = a.mask + size_t(row) * a.mask_stride + (c.begin >> 5);
+    for (int w = c.tid; w < (c.len + 31) / 32; w += kThreads) s->mask_words[w] = __ldg(mw + w);
+  }
+  // ---- history counts (16-bit counters packed in pairs; remote shared-memory atomics route each id to its owner)
+  const bool penalised = a.history != nullptr && (a.repetition != 1.f || a.presence != 0.f || a.frequency != 0.f);
+  int hist_len = penalised ? (a.history_len ? a.history_len[row] : int(a.history_stride)) : 0;
+  const bool bad_history = hist_len < 0 || hist_len > 65535;
+  if (bad_history) hist_len = 0;
+  if (hist_len > 0) {
+    for (int j = c.tid; j < kSliceCap / 2; j += kThreads) s->u.count_pairs[j] = 0;
+    c.cluster.sync();
+    const int32_t *h = a.history + size_t(row) * a.history_stride;
+    const int per = (hist_len + c.nranks - 1) / c.nranks;
+    const int h0 = min(hist_len, c.rank * per), h1 = min(hist_len, h0 + per);
+    for (int base = h0 + c.warp * 32; base < h1; base += kThreads) {
+      const int i = base + c.lane;
+      const int id = i < h1 ? __ldg(h + i) : -1;
+      const bool valid = id >= 0 && id < a.vocab;
+      const unsigned peers = __match_any_sync(0xffffffffu, valid ? id : -1);
+      if (valid && c.lane == __ffs(peers) - 1) {
+        const int owner = id / c.stride_ids, local = id - owner * c.stride_ids;
+        atomicAdd(c.cluster.map_shared_rank(&s->u.count_pairs[local >> 1], owner),
+                  uint32_t(__popc(peers)) << ((local & 1) * 16));
+      }
+    }
+    c.cluster.sync();
+  }
+  const bool landed = stage_wait(c, used_tma);
+
+  // ---- effective logits, first maximum, allowed count
+  int flags = (landed ? 0 : 8) | (bad_history ? 4 : 0);
+  float best = -CUDART_INF_F;
+  int best_id = 0x7fffffff, allowed = 0;
+  for (int it = 0; it < c.region; it += 32) {
+    const int j = c.warp * c.region + it + c.lane;
+    if (j >= c.len) continue;
+    float x = s->y[j];
+    if ((__float_as_uint(x) & 0x7f800000u) == 0x7f800000u) flags |= 1;
+    if (hist_len > 0) {
+      const uint32_t cnt = (s->u.count_pairs[j >> 1] >> ((j & 1) * 16)) & 0xffffu;
+      if (cnt) {
+        const float v = x > 0.f ? __fdiv_rn(x, a.repetition) : __fmul_rn(x, a.repetition);
+        x = __fsub_rn(v, __fadd_rn(a.presence, __fmul_rn(a.frequency, float(cnt))));
+        if ((__float_as_uint(x) & 0x7f800000u) == 0x7f800000u) flags |= 2;
+      }
+    }
+    const bool ok = !a.mask || ((s->mask_words[j >> 5] >> (j & 31)) & 1u);
+    if (!ok) x = -CUDART_INF_F;
+    s->y[j] = x;
+    if (ok) {
+      ++allowed;
+      if (x > best) { best = x; best_id = c.begin + j; }
+    }
+  }
+  __syncthreads();
+  {
+    Slot mine{};
+    block_argmax(c, best, best_id);
+    mine.f[0] = best; mine.i[0] = best_id;
+    mine.i[1] = block_or(c, flags);
+    mine.i[2] = block_sum(c, allowed);
+    const Slot *all = exchange(c, mine);
+    best = all[0].f[0]; best_id = all[0].i[0]; flags = all[0].i[1]; allowed = all[0].i[2];
+    for (int r = 1; r < c.nranks; ++r) {
+      if (all[r].f[0] > best || (all[r].f[0] == best && all[r].i[0] < best_id)) { best = all[r].f[0]; best_id = all[r].i[0]; }
+      flags |= all[r].i[1];
+      allowed += all[r].i[2];
+    }
+  }
+  int status = 0;
+  if (flags & 8) status = -5;
+  else if (flags & 1) status = -1;
+  else if (flags & 4) status = -7;
+  else if (flags & 2) status = -3;
+  else if (allowed == 0) status = -2;
+
+  const float max_logit = best;
+  const double t = a.temperature;
+  auto weight = [max_logit, t](float y) { return exp((double(y) - double(max_logit)) / t); };
+  Cut cut{-CUDART_INF_F, -1};
+  int entered = allowed, kept = allowed;
+  double z = 0, e_kept = 0;
+  int token = -1;
+
+  if (status == 0 && t == 0) {
+    token = best_id;
+    kept = 1; z = 1; e_kept = 1;
+    cut.y = max_logit; cut.id = best_id;
+  } else if (status == 0) {
+    // ---- top-k
+    if (a.top_k > 0 && a.top_k < allowed) {
+      CutResult r = find_cut<false>(c, max_logit, 16.f / kBins, a.top_k, 0.0, allowed,
+                                    [](float y, int) { return y > -CUDART_INF_F; }, weight);
+      if (r.error) status = r.error;
+      else { cut = r.cut; entered = kept = a.top_k; }
+    }
+    const Cut base = cut;
+    // ---- normaliser and top-p
+    if (status == 0 && a.top_p < 1.0) {
+      CutResult r = find_cut<true>(c, max_logit, float(48.0 * t) / kBins, 0, a.top_p, entered,
+                                   [base](float y, int id) { return survives(y, id, base); }, weight);
+      if (r.error) status = r.error;
+      else {
+        z = r.z; e_kept = r.e_kept; kept = r.kept;
+        if (r.cut.id >= 0) cut = r.cut;
+        if (r.ambiguous) status |= 2;
+      }
+      if (status >= 0 && kMode == kModeSample) region_sums(c, cut, weight);
+    } else if (status == 0) {
+      region_sums(c, cut, weight);
+      double block_total = 0;
+      for (int w = 0; w < kWarps; ++w) block_total += s->warp_sum[w];
+      Slot mine{};
+      mine.d[0] = block_total;
+      const Slot *all = exchange(c, mine);
+      for (int r = 0; r < c.nranks; ++r) z += all[r].d[0];
+      e_kept = z;
+    }
+    if (status >= 0 && kMode == kModeSample) {
+      const double u = philox_uniform(a.seeds[row], a.steps[row], a.slot, a.purpose);
+      int amb = 0;
+      token = draw_token(c, cut, u, (2.0 * kept + 256.0) * kU, weight, &amb);
+      if (amb) status |= 1;
+    }
+  }
+  if (c.rank == 0 && c.tid == 0) {
+    if (kMode == kModeSample) {
+      a.tokens[row] = status < 0 ? -1 : token;
+      if (a.status) a.status[row] = status;
+    } else {
+      RowStats st;
+      st.z = z; st.e_kept = e_kept; st.max_logit = max_logit; st.argmax = best_id; st.cut = cut;
+      st.kept = kept; st.entered = entered; st.status = status; st.pad = 0;
+      a.stats[row] = st;
+    }
+  }
+  // no CTA may exit while a peer can still address its shared memory
+  c.cluster.sync();
+}
+
+}  // namespace ds41

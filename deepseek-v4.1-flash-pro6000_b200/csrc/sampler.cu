@@ -1,0 +1,79 @@
+// C-ABI entry points of the sampler and of the host-side Philox helpers.  See include/ds41_b200.h.
+#include "ds41_b200.h"
+#include "row_kernel.cuh"
+#include "host_error.h"
+#include <cmath>
+
+namespace ds41 {
+
+int cluster_size_for(int vocab) {
+  int n = 1;
+  while (n < kMaxCluster && vocab > n * kSliceCap) n <<= 1;
+  // more CTAs per row than strictly needed keep the per-CTA slice short (latency) once the row is large
+  if (vocab > 32768) n = kMaxCluster;
+  return n;
+}
+
+template <int kMode>
+cudaError_t launch_rows(const RowArgs &a, int rows, cudaStream_t stream) {
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (configured_device != dev) {
+    e = cudaFuncSetAttribute(row_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(RowSmem)));
+    if (e != cudaSuccess) return e;
+    configured_device = dev;
+  }
+  const int cl = cluster_size_for(a.vocab);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(unsigned(rows) * cl);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = sizeof(RowSmem);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cl; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, row_kernel<kMode>, a);
+}
+template cudaError_t launch_rows<kModeSample>(const RowArgs &, int, cudaStream_t);
+template cudaError_t launch_rows<kModeStats>(const RowArgs &, int, cudaStream_t);
+
+}  // namespace ds41
+
+using namespace ds41;
+
+extern "C" uint32_t ds41_spark_rng_word_v2(uint64_t seed, uint64_t step, uint32_t slot, uint32_t purpose, uint64_t draw) {
+  if (slot > 5 || purpose > 3 || draw / 4 > UINT32_MAX) { set_error("Philox v2 address out of range"); return 0; }
+  return philox_word(seed, step, slot, purpose, draw);
+}
+extern "C" double ds41_spark_uniform_v2(uint64_t seed, uint64_t step, uint32_t slot, uint32_t purpose, uint64_t draw) {
+  if (slot > 5 || purpose > 3 || draw > 8589934591ULL) { set_error("Philox v2 address out of range"); return NAN; }
+  return philox_uniform(seed, step, slot, purpose, draw);
+}
+extern "C" const char *ds41_spark_error(void) { return last_error(); }
+
+extern "C" int ds41_b200_sample_logits(const ds41_b200_sample_args *p, cudaStream_t stream) {
+  if (!p || p->struct_bytes != sizeof(ds41_b200_sample_args)) return invalid("sample args: struct size / ABI mismatch");
+  if (p->rows < 1 || p->vocab < 1 || p->vocab > DS41_B200_MAX_VOCAB) return invalid("sample args: rows/vocab out of range");
+  if (!p->logits || (p->logits_stride < p->vocab && p->logits_stride != 0) || !p->seeds || !p->steps || !p->tokens) return invalid("sample args: null buffer or short stride");
+  if (!std::isfinite(p->temperature) || p->temperature < 0 || !std::isfinite(p->top_p) || p->top_p <= 0 || p->top_p > 1)
+    return invalid("temperature/top_p/logits");
+  if (p->top_k < 0 || !(p->repetition > 0) || !std::isfinite(p->repetition) || !std::isfinite(p->presence) || !std::isfinite(p->frequency))
+    return invalid("penalty/top_k arguments");
+  if (p->slot > 5 || p->purpose > 3) return invalid("Philox v2 address out of range");
+  if (p->history && (p->history_stride < 0 || (!p->history_len && p->history_stride > DS41_B200_MAX_HISTORY)))
+    return invalid("history longer than DS41_B200_MAX_HISTORY");
+  if (p->mask && p->mask_stride < (p->vocab + 31) / 32) return invalid("mask stride shorter than the vocabulary");
+  RowArgs a{};
+  a.logits = p->logits; a.logits_stride = p->logits_stride; a.vocab = p->vocab;
+  a.temperature = p->temperature > 0 ? std::fmax(p->temperature, 1e-5) : 0.0;  // engine/src/sampling.cpp:209-210
+  a.top_p = p->top_p; a.top_k = p->top_k;
+  a.repetition = p->repetition; a.presence = p->presence; a.frequency = p->frequency;
+  a.history = p->history; a.history_stride = p->history_stride; a.history_len = p->history_len;
+  a.mask = p->mask; a.mask_stride = p->mask_stride;
+  a.seeds = p->seeds; a.steps = p->steps; a.slot = p->slot; a.purpose = p->purpose;
+  a.tokens = p->tokens; a.status = p->status; a.stats = nullptr;
+  return int(launch_rows<kModeSample>(a, p->rows, stream));
+}

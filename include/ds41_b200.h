@@ -1,0 +1,112 @@
+/* ds41_b200.h -- C ABI of the B200 (sm_100a) decode-tail library: LM head -> sampler -> MTP verify.
+ *
+ * Conventions are the reference plugins' own (components/fuse-head/include/ds41/fuse_head.h:8,
+ * components/dense/include/ds41/dense.h:8-10, engine/third_party/spark/include/ds41/spark.h:35-36,116-120):
+ *   - every tensor argument is DEVICE memory owned by the caller and alive until the stream reaches the call;
+ *   - calls only enqueue work on the given stream: no allocation, no synchronisation, no hidden state;
+ *   - the return value is a cudaError_t as int (0 = enqueued); argument errors return cudaErrorInvalidValue and
+ *     leave a message for ds41_spark_error();
+ *   - DATA errors (non-finite logits, empty allowed set, impossible draft ...) are reported in band, per row,
+ *     in the caller's status / result buffers, exactly as the reference GPU sampler signals `emitted = -1`
+ *     (third_party/spark/src/sampling.cu:29-32).
+ * There is no CPU implementation behind any entry point; a machine without a CUDA device gets a CUDA error.
+ */
+#ifndef DS41_B200_H
+#define DS41_B200_H
+#include <stddef.h>
+#include <stdint.h>
+#include <cuda_runtime_api.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DS41_B200_ABI 1
+#define DS41_B200_MAX_VOCAB 131072 /* 8 cluster CTAs x 16384 staged logits */
+#define DS41_B200_MAX_HISTORY 65535 /* 16-bit shared-memory counters */
+
+/* ---- per-row status words written by the sampler / verifier ------------------------------------------------
+ * 0            decision certified: it provably equals the reference FP64 rule for these inputs, assuming only
+ *              that both exp() implementations are within 1 ulp.
+ * >0 bit set   decision taken but NOT certified (the quantity compared lay inside the rounding-error bound of
+ *              the parallel summation): 1 inverse-CDF draw, 2 top-p cut, 4 accept test, 8 residual draw.
+ * <0           row rejected, token = -1 / emitted = -1:  */
+#define DS41_B200_ROW_NONFINITE (-1)      /* a logit is NaN/Inf   (sampling.cpp:32 "nonfinite logits") */
+#define DS41_B200_ROW_EMPTY (-2)          /* bitmask allows no id (sampling.cpp:19 "empty residual support") */
+#define DS41_B200_ROW_PENALTY_OVERFLOW (-3)
+#define DS41_B200_ROW_TIES (-4)           /* more than 1024 equal logits straddle a top-k / top-p cut */
+#define DS41_B200_ROW_TIMEOUT (-5)        /* a bounded device-side wait expired */
+#define DS41_B200_ROW_DRAFT (-6)          /* draft id out of range or impossible under q (sampling.cpp:44,47) */
+#define DS41_B200_ROW_HISTORY (-7)        /* history_len[r] negative or above DS41_B200_MAX_HISTORY */
+
+/* Same layout as ds41_spark_result (spark.h:106-108). */
+typedef struct ds41_spark_result {
+  int32_t tokens[6];
+  int emitted, accepted_drafts, accepted_input_rows, rejected;
+} ds41_spark_result;
+
+/* ---- host-side helpers (pure integer/FP64 arithmetic, no device) --------------------------------------------
+ * Replace ds41_spark_rng_word_v2 / ds41_spark_uniform_v2 / ds41_spark_error (spark.h:39,129-130; implementation
+ * third_party/spark/src/sampling.cpp:9-10,57-58).  Invalid addresses return 0 / NaN and set the message. */
+uint32_t ds41_spark_rng_word_v2(uint64_t seed, uint64_t step, uint32_t slot, uint32_t purpose, uint64_t draw);
+double ds41_spark_uniform_v2(uint64_t seed, uint64_t step, uint32_t slot, uint32_t purpose, uint64_t draw);
+const char *ds41_spark_error(void);
+
+/* ---- sampler: logits -> token ids -----------------------------------------------------------------------
+ * Replaces, fused and batched on the device, the engine's per-token host sequence
+ *   probabilities(logits, T, top_p)  (engine/src/sampling.cpp:205-219 -> spark sampling.cpp:30-38)
+ *   sample(p, rng, step, slot, purpose) (engine/src/sampling.cpp:220-226 -> spark sampling.cpp:18-21,59)
+ *   argmax(logits) for temperature 0   (engine/src/sampling.cpp:133-139; server.cpp:623-625)
+ * Row r draws with the Philox address (seeds[r], steps[r], slot, purpose) (spark_rng.h:23-36).
+ * The temperature floor max(T,1e-5) of the adapter is applied here (engine/src/sampling.cpp:209-210).
+ * top_k, the three penalties and the bitmask have no counterpart in the reference; their rule is stated in
+ * DESIGN.md and implemented identically by the CPU oracle. */
+typedef struct ds41_b200_sample_args {
+  uint32_t struct_bytes;      /* sizeof(ds41_b200_sample_args): ABI check */
+  int32_t rows, vocab;        /* 1 <= vocab <= DS41_B200_MAX_VOCAB */
+  const float *logits;        /* [rows, logits_stride] fp32 */
+  int64_t logits_stride;      /* elements between rows: >= vocab, or 0 to give every row the same logits */
+  double temperature;         /* >= 0, finite; 0 = greedy */
+  double top_p;               /* (0,1] */
+  int32_t top_k;              /* 0 = off */
+  float repetition, presence, frequency; /* 1,0,0 = off */
+  const int32_t *history;     /* [rows, history_stride] token ids or NULL; ids outside [0,vocab) are padding */
+  int64_t history_stride;
+  const int32_t *history_len; /* [rows] valid entries per row, or NULL = history_stride for every row */
+  const uint32_t *mask;       /* [rows, mask_stride] allowed-token bits (id/32, id%32) or NULL */
+  int64_t mask_stride;
+  const uint64_t *seeds;      /* [rows] Philox key per row */
+  const uint64_t *steps;      /* [rows] attempt counter per row */
+  uint32_t slot, purpose;     /* slot 0..5, purpose 0..3 (spark.h:96) */
+  int32_t *tokens;            /* [rows] out */
+  int32_t *status;            /* [rows] out, see above; may be NULL */
+} ds41_b200_sample_args;
+int ds41_b200_sample_logits(const ds41_b200_sample_args *args, cudaStream_t stream);
+
+/* ---- MTP speculative verification from logits ---------------------------------------------------------------
+ * Replaces probabilities_rows() + reject_sample() (engine/src/speculation.cpp:179-182;
+ * engine/src/sampling.cpp:142-204,227-275 -> ds41_spark_verify_v2, spark sampling.cpp:39-56) for `sequences`
+ * independent transactions of `drafts` (0..5) proposals each.  p rows come from the target logits, q rows from
+ * the draft logits, both through the same temperature/top-p rule, so q is the measure the proposal was drawn
+ * from (spark.h:101-105).  Sequence s uses the address (seeds[s], steps[s], slot = position, purpose =
+ * ACCEPT / RESIDUAL / TARGET) exactly as the reference.  temperature 0 selects the greedy rule (draft_logits
+ * may then be NULL).  `scratch` is caller-owned device memory of ds41_b200_verify_scratch_bytes() bytes. */
+typedef struct ds41_b200_verify_args {
+  uint32_t struct_bytes;
+  int32_t sequences, drafts, vocab;
+  const float *target_logits;  /* [sequences*(drafts+1), vocab] */
+  const float *draft_logits;   /* [sequences*drafts, vocab] */
+  const int32_t *draft_ids;    /* [sequences*drafts] */
+  double temperature, top_p;
+  const uint64_t *seeds, *steps; /* [sequences] */
+  ds41_spark_result *results;  /* [sequences] out */
+  int32_t *status;             /* [sequences] out, may be NULL */
+  void *scratch;
+  size_t scratch_bytes;
+} ds41_b200_verify_args;
+size_t ds41_b200_verify_scratch_bytes(int sequences, int drafts);
+int ds41_b200_verify_logits(const ds41_b200_verify_args *args, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
