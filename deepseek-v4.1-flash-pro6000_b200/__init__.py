@@ -70,6 +70,9 @@ def lib():
         L.ds41_spark_uniform_v2.restype = _f64
         L.ds41_spark_uniform_v2.argtypes = [_u64, _u64, _u32, _u32, _u64]
         L.ds41_b200_sample_logits.argtypes = [C.POINTER(SampleArgs), _P]
+        L.ds41_b200_verify_logits.argtypes = [C.POINTER(VerifyArgs), _P]
+        L.ds41_b200_verify_scratch_bytes.restype = C.c_size_t
+        L.ds41_b200_verify_scratch_bytes.argtypes = [C.c_int, C.c_int]
         _lib = L
     return _lib
 
@@ -165,3 +168,50 @@ def sample_logits(logits, temperature, top_p, seeds, steps, slot=0, purpose=Purp
     with torch.cuda.device(logits.device):
         _check(lib().ds41_b200_sample_logits(C.byref(a), _stream()), "ds41_b200_sample_logits")
     return tokens, status
+
+
+def verify_scratch_bytes(sequences, drafts):
+    return lib().ds41_b200_verify_scratch_bytes(sequences, drafts)
+
+
+def verify_logits(target_logits, draft_logits, draft_ids, drafts, temperature, top_p, seeds, steps, scratch=None,
+                  results=None, status=None):
+    """Batched probabilities_rows() + reject_sample() (engine/src/speculation.cpp:179-182) on device logits.
+
+    target_logits [sequences*(drafts+1), vocab], draft_logits [sequences*drafts, vocab] (None when greedy or no
+    drafts), draft_ids int32 [sequences*drafts].  Returns (results, status): results is a uint8 CUDA tensor holding
+    `sequences` ds41_spark_result records (view it with RESULT_DTYPE on the host)."""
+    target_logits = _dev(target_logits, torch.float32, "target_logits")
+    draft_logits = _dev(draft_logits, torch.float32, "draft_logits")
+    draft_ids = _dev(draft_ids, torch.int32, "draft_ids")
+    seeds = _dev(seeds, torch.int64, "seeds")
+    steps = _dev(steps, torch.int64, "steps")
+    rows, vocab = target_logits.shape
+    if rows % (drafts + 1):
+        raise ValueError("speculative row count")
+    sequences = rows // (drafts + 1)
+    device = target_logits.device
+    need = verify_scratch_bytes(sequences, drafts)
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.uint8, device=device)
+    if results is None:
+        results = torch.empty(sequences * C.sizeof(SparkResult), dtype=torch.uint8, device=device)
+    if status is None:
+        status = torch.empty(sequences, dtype=torch.int32, device=device)
+    a = VerifyArgs()
+    a.struct_bytes = C.sizeof(VerifyArgs)
+    a.sequences, a.drafts, a.vocab = sequences, drafts, vocab
+    a.target_logits = target_logits.data_ptr()
+    a.draft_logits = draft_logits.data_ptr() if draft_logits is not None else None
+    a.draft_ids = draft_ids.data_ptr() if draft_ids is not None else None
+    a.temperature, a.top_p = temperature, top_p
+    a.seeds, a.steps = seeds.data_ptr(), steps.data_ptr()
+    a.results, a.status = results.data_ptr(), status.data_ptr()
+    a.scratch, a.scratch_bytes = scratch.data_ptr(), scratch.numel()
+    with torch.cuda.device(device):
+        _check(lib().ds41_b200_verify_logits(C.byref(a), _stream()), "ds41_b200_verify_logits")
+    return results, status
+
+
+def results_to_numpy(results):
+    return np.frombuffer(results.cpu().numpy().tobytes(), dtype=RESULT_DTYPE)

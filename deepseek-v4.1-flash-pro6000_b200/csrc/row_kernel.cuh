@@ -27,17 +27,15 @@ struct RowArgs {
   RowStats *stats;
 };
 
-// Sum of exp over the survivors of `cut` in this warp's region, lanes striding the region in id order; the warp
-// total lands in warp_sum[warp].  Fixed order => the same bits every run.
-template <class Weight>
-__device__ __forceinline__ void region_sums(RowCtx &c, Cut cut, Weight weight) {
+// Region sums of a non-negative per-id value (value(j) for local index j < len, 0 for ids outside the support):
+// lanes stride the warp's region in id order, the warp total lands in warp_sum[warp].  Fixed order => same bits
+// every run.
+template <class Value>
+__device__ __forceinline__ void region_sums(RowCtx &c, Value value) {
   double acc = 0;
   for (int it = 0; it < c.region; it += 32) {
     const int j = c.warp * c.region + it + c.lane;
-    if (j < c.len) {
-      const float y = c.s->y[j];
-      if (survives(y, c.begin + j, cut)) acc += weight(y);
-    }
+    if (j < c.len) acc += value(j);
   }
 #pragma unroll
   for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -45,12 +43,15 @@ __device__ __forceinline__ void region_sums(RowCtx &c, Cut cut, Weight weight) {
   __syncthreads();
 }
 
-// Inverse CDF in id order over the survivors (reference: draw(), third_party/spark/src/sampling.cpp:18-21).
-// warp_sum[] must hold the region sums.  Returns the token to every thread; *ambiguous is set when the uniform lies
-// within rel_bound * total of a CDF step on either side of the chosen id.
-template <class Weight>
-__device__ int draw_token(RowCtx &c, Cut cut, double u, double rel_bound, Weight weight, int *ambiguous) {
+// Inverse CDF in id order (reference: draw(), third_party/spark/src/sampling.cpp:18-21): the first id whose running
+// sum exceeds u * total, else the last id with a positive value.  warp_sum[] must hold the region sums of `value`.
+// Returns the token to every thread of every CTA; *ambiguous is set when the target lies within
+// rel_bound*total + abs_bound of a CDF step on either side of the chosen id; *total_out receives the total.
+template <class Value>
+__device__ int draw_token(RowCtx &c, double u, double rel_bound, double abs_bound, Value value, int *ambiguous,
+                          double *total_out) {
   RowSmem *s = c.s;
+  if (c.tid == 0) s->bcast_i[2] = 0;
   double block_total = 0;
   for (int w = 0; w < kWarps; ++w) block_total += s->warp_sum[w];
   Slot mine{};
@@ -61,8 +62,9 @@ __device__ int draw_token(RowCtx &c, Cut cut, double u, double rel_bound, Weight
     if (r == c.rank) prefix = total;
     total += all[r].d[0];
   }
+  *total_out = total;
   const double target = u * total;
-  const double slack = rel_bound * total;
+  const double slack = rel_bound * total + abs_bound;
   double inner = 0;
   for (int w = 0; w < c.warp; ++w) inner += s->warp_sum[w];
   const double start = prefix + inner, end = prefix + (inner + s->warp_sum[c.warp]);
@@ -72,11 +74,7 @@ __device__ int draw_token(RowCtx &c, Cut cut, double u, double rel_bound, Weight
     int last_positive = -1;
     for (int it = 0; it < c.region && found < 0; it += 32) {
       const int j = c.warp * c.region + it + c.lane;
-      double v = 0;
-      if (j < c.len) {
-        const float y = s->y[j];
-        if (survives(y, c.begin + j, cut)) v = weight(y);
-      }
+      const double v = j < c.len ? value(j) : 0.0;
       double scan = v;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -115,10 +113,7 @@ __device__ int draw_token(RowCtx &c, Cut cut, double u, double rel_bound, Weight
     int last = -1;
     for (int it = 0; it < c.region; it += 32) {
       const int j = c.warp * c.region + it + c.lane;
-      if (j < c.len) {
-        const float y = s->y[j];
-        if (survives(y, c.begin + j, cut) && weight(y) > 0) last = max(last, c.begin + j);
-      }
+      if (j < c.len && value(j) > 0) last = max(last, c.begin + j);
     }
     Slot m2{};
     m2.i[0] = block_max(c, last);
@@ -138,7 +133,6 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
   const int row = blockIdx.x / c.nranks;
   const float *logits = a.logits + size_t(row) * a.logits_stride;
 
-  if (c.tid == 0) s->bcast_i[2] = 0;
   bool used_tma;
   stage_begin(c, logits, used_tma);
   if (a.mask) {
@@ -222,6 +216,11 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
   const double t = a.temperature;
   auto weight = [max_logit, t](float y) { return exp((double(y) - double(max_logit)) / t); };
   Cut cut{-CUDART_INF_F, -1};
+  // value of local id j for the sums and the draw: exp weight of a survivor of the CURRENT cut, else 0
+  auto value = [&cut, &c, s, weight](int j) {
+    const float y = s->y[j];
+    return survives(y, c.begin + j, cut) ? weight(y) : 0.0;
+  };
   int entered = allowed, kept = allowed;
   double z = 0, e_kept = 0;
   int token = -1;
@@ -249,9 +248,9 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
         if (r.cut.id >= 0) cut = r.cut;
         if (r.ambiguous) status |= 2;
       }
-      if (status >= 0 && kMode == kModeSample) region_sums(c, cut, weight);
+      if (status >= 0 && kMode == kModeSample) region_sums(c, value);
     } else if (status == 0) {
-      region_sums(c, cut, weight);
+      region_sums(c, value);
       double block_total = 0;
       for (int w = 0; w < kWarps; ++w) block_total += s->warp_sum[w];
       Slot mine{};
@@ -263,7 +262,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
     if (status >= 0 && kMode == kModeSample) {
       const double u = philox_uniform(a.seeds[row], a.steps[row], a.slot, a.purpose);
       int amb = 0;
-      token = draw_token(c, cut, u, (2.0 * kept + 256.0) * kU, weight, &amb);
+      double total;
+      token = draw_token(c, u, (2.0 * kept + 256.0) * kU, 0.0, value, &amb, &total);
       if (amb) status |= 1;
     }
   }

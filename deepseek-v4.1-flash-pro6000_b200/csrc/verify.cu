@@ -1,0 +1,181 @@
+// Speculative verification from logits (MTP accept / resample), batched over sequences.
+//
+// Rule reproduced: verify_impl, engine/third_party/spark/src/sampling.cpp:39-53, with p and q rows produced by the
+// sampler's probability rule (engine/src/sampling.cpp:142-219), i.e. the sequence
+//   probabilities_rows(target) ; probabilities(draft_k) ; reject_sample(...)   (engine/src/speculation.cpp:126-182).
+// Two launches:
+//   1. row statistics for every target and draft row (row_kernel<kModeStats>): first maximum, normaliser, top-p cut
+//      and kept mass, written to caller-provided scratch;
+//   2. one cluster per sequence walks the positions: accept test from the two rows' statistics and the two logits at
+//      the draft id; on the first rejection the residual max(0,p-q) is drawn by an inverse CDF streamed from the two
+//      rows (normally still L2 resident), otherwise the bonus token is drawn from the last target row.
+#include "ds41_b200.h"
+#include "host_error.h"
+#include "row_kernel.cuh"
+#include <cmath>
+
+namespace ds41 {
+
+template <int kMode>
+cudaError_t launch_rows(const RowArgs &a, int rows, cudaStream_t stream);
+int cluster_size_for(int vocab);
+
+struct VerifyArgs {
+  const float *target, *draft;
+  const int32_t *ids;
+  const RowStats *pstats, *qstats;
+  int drafts, vocab;
+  double temperature;
+  const uint64_t *seeds, *steps;
+  ds41_spark_result *results;
+  int32_t *status;
+};
+
+struct Measure {  // one row's probability measure: P(id) = survives ? exp((x-max)/T) / e_kept : 0
+  const float *x;
+  RowStats st;
+  double t;
+  __device__ __forceinline__ double at(int id) const {
+    const float y = __ldg(x + id);
+    return survives(y, id, st.cut) ? exp((double(y) - double(st.max_logit)) / t) / st.e_kept : 0.0;
+  }
+  __device__ __forceinline__ double bound() const { return 2.0 * (double(st.kept) + 64.0) * kU; }
+};
+
+__global__ void __launch_bounds__(kThreads, 2) verify_kernel(VerifyArgs a) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  RowSmem *s = reinterpret_cast<RowSmem *>(smem_raw);
+  RowCtx c = make_ctx(s, a.vocab);
+  const int seq = blockIdx.x / c.nranks;
+  const int D = a.drafts;
+  const bool greedy = a.temperature == 0;
+  const uint64_t seed = a.seeds[seq], step = a.steps[seq];
+  ds41_spark_result r{};
+  int status = 0;
+  // any rejected row of this transaction rejects the transaction (the reference computes every p and q row first)
+  for (int k = 0; k <= D; ++k) {
+    const int st = a.pstats[size_t(seq) * (D + 1) + k].status;
+    if (st < 0 && status >= 0) status = st;
+    else if (st > 0 && status >= 0) status |= st;
+  }
+  if (!greedy)
+    for (int k = 0; k < D; ++k) {
+      const int st = a.qstats[size_t(seq) * D + k].status;
+      if (st < 0 && status >= 0) status = st;
+      else if (st > 0 && status >= 0) status |= st;
+    }
+  for (int k = 0; k < D && status >= 0 && !r.rejected; ++k) {
+    const int d = a.ids[size_t(seq) * D + k];
+    if (d < 0 || d >= a.vocab) { status = -6; break; }  // checked only when the position is reached (sampling.cpp:44)
+    Measure P{a.target + (size_t(seq) * (D + 1) + k) * a.vocab, a.pstats[size_t(seq) * (D + 1) + k], a.temperature};
+    bool accept;
+    if (greedy) {
+      accept = d == P.st.argmax;
+      if (!accept) { r.tokens[r.emitted++] = P.st.argmax; r.rejected = 1; }
+    } else {
+      Measure Q{a.draft + (size_t(seq) * D + k) * a.vocab, a.qstats[size_t(seq) * D + k], a.temperature};
+      const double pd = P.at(d), qd = Q.at(d);
+      if (!(qd > 0)) { status = -6; break; }
+      const double ratio = fmin(1.0, pd / qd);
+      const double u = philox_uniform(seed, step, uint32_t(k), 2);
+      accept = u < ratio;
+      if (ratio < 1.0 && fabs(u - ratio) <= (P.bound() + Q.bound() + 16 * kU) * ratio) status |= 4;
+      if (!accept) {
+        // residual draw: inverse CDF over max(0, P - Q) in id order
+        auto value = [&](int j) { const int id = c.begin + j; return fmax(0.0, P.at(id) - Q.at(id)); };
+        region_sums(c, value);
+        int amb = 0;
+        double total = 0;
+        const int support = min(a.vocab, P.st.kept + Q.st.kept);
+        const int token = draw_token(c, philox_uniform(seed, step, uint32_t(k), 3), (2.0 * support + 256.0) * kU,
+                                     P.bound() + Q.bound(), value, &amb, &total);
+        if (!(total > 0) || token < 0) { status = -2; break; }
+        if (amb) status |= 8;
+        r.tokens[r.emitted++] = token;
+        r.rejected = 1;
+      }
+    }
+    if (accept) { r.tokens[r.emitted++] = d; ++r.accepted_drafts; }
+  }
+  if (status >= 0 && !r.rejected) {
+    Measure P{a.target + (size_t(seq) * (D + 1) + D) * a.vocab, a.pstats[size_t(seq) * (D + 1) + D], a.temperature};
+    if (greedy) {
+      r.tokens[r.emitted++] = P.st.argmax;
+    } else {
+      auto value = [&](int j) { return P.at(c.begin + j) * P.st.e_kept; };  // unnormalised weights, as the sampler
+      region_sums(c, value);
+      int amb = 0;
+      double total = 0;
+      const int token = draw_token(c, philox_uniform(seed, step, uint32_t(D), 0), (2.0 * P.st.kept + 256.0) * kU, 0.0,
+                                   value, &amb, &total);
+      if (amb) status |= 1;
+      r.tokens[r.emitted++] = token;
+    }
+  }
+  r.accepted_input_rows = r.accepted_drafts + 1;
+  if (status < 0) { r = ds41_spark_result{}; r.emitted = -1; }
+  if (c.rank == 0 && c.tid == 0) {
+    a.results[seq] = r;
+    if (a.status) a.status[seq] = status;
+  }
+  c.cluster.sync();
+}
+
+}  // namespace ds41
+
+using namespace ds41;
+
+extern "C" size_t ds41_b200_verify_scratch_bytes(int sequences, int drafts) {
+  if (sequences < 1 || drafts < 0 || drafts > 5) return 0;
+  return size_t(sequences) * size_t(2 * drafts + 1) * sizeof(RowStats);
+}
+
+extern "C" int ds41_b200_verify_logits(const ds41_b200_verify_args *p, cudaStream_t stream) {
+  if (!p || p->struct_bytes != sizeof(ds41_b200_verify_args)) return invalid("verify args: struct size / ABI mismatch");
+  if (p->sequences < 1 || p->drafts < 0 || p->drafts > 5 || p->vocab < 1 || p->vocab > DS41_B200_MAX_VOCAB)
+    return invalid("verify arguments");
+  if (!std::isfinite(p->temperature) || p->temperature < 0 || !std::isfinite(p->top_p) || p->top_p <= 0 || p->top_p > 1)
+    return invalid("temperature/top_p/logits");
+  const bool greedy = p->temperature == 0;
+  if (!p->target_logits || !p->seeds || !p->steps || !p->results ||
+      (p->drafts && (!p->draft_ids || (!p->draft_logits && !greedy))))
+    return invalid("verify arguments");
+  if (!p->scratch || p->scratch_bytes < ds41_b200_verify_scratch_bytes(p->sequences, p->drafts) ||
+      (reinterpret_cast<uintptr_t>(p->scratch) & 15u))
+    return invalid("verify scratch too small or misaligned");
+  RowStats *pstats = static_cast<RowStats *>(p->scratch);
+  RowStats *qstats = pstats + size_t(p->sequences) * (p->drafts + 1);
+  RowArgs a{};
+  a.vocab = p->vocab; a.logits_stride = p->vocab;
+  a.temperature = p->temperature > 0 ? std::fmax(p->temperature, 1e-5) : 0.0;
+  a.top_p = p->top_p; a.top_k = 0; a.repetition = 1.f;
+  a.logits = p->target_logits; a.stats = pstats;
+  cudaError_t e = launch_rows<kModeStats>(a, p->sequences * (p->drafts + 1), stream);
+  if (e != cudaSuccess) return int(e);
+  if (p->drafts && !greedy) {
+    a.logits = p->draft_logits; a.stats = qstats;
+    e = launch_rows<kModeStats>(a, p->sequences * p->drafts, stream);
+    if (e != cudaSuccess) return int(e);
+  }
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return int(e);
+  if (configured_device != dev) {
+    e = cudaFuncSetAttribute(verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(RowSmem)));
+    if (e != cudaSuccess) return int(e);
+    configured_device = dev;
+  }
+  VerifyArgs v{p->target_logits, p->draft_logits, p->draft_ids, pstats, qstats, p->drafts, p->vocab, a.temperature,
+               p->seeds, p->steps, p->results, p->status};
+  const int cl = cluster_size_for(p->vocab);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(unsigned(p->sequences) * cl);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = sizeof(RowSmem);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cl; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return int(cudaLaunchKernelEx(&cfg, verify_kernel, v));
+}
