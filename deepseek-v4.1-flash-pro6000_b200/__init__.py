@@ -71,6 +71,11 @@ def lib():
         L.ds41_spark_uniform_v2.argtypes = [_u64, _u64, _u32, _u32, _u64]
         L.ds41_b200_sample_logits.argtypes = [C.POINTER(SampleArgs), _P]
         L.ds41_b200_verify_logits.argtypes = [C.POINTER(VerifyArgs), _P]
+        L.ds41_b200_quantize_activations.argtypes = [_P, _P, _P, C.c_int, C.c_int, _P]
+        L.ds41_b200_head_fp8.argtypes = [_P, _P, _P, _P, _P, _i64, C.c_int, C.c_int, C.c_int, _P, _P]
+        L.ds41_fuse_head_fp8_workspace_bytes.restype = C.c_size_t
+        L.ds41_fuse_head_fp8_workspace_bytes.argtypes = [C.c_int, C.c_int]
+        L.ds41_fuse_head_fp8.argtypes = [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, _P, C.c_size_t, _P, _P]
         L.ds41_b200_verify_scratch_bytes.restype = C.c_size_t
         L.ds41_b200_verify_scratch_bytes.argtypes = [C.c_int, C.c_int]
         _lib = L
@@ -215,3 +220,56 @@ def verify_logits(target_logits, draft_logits, draft_ids, drafts, temperature, t
 
 def results_to_numpy(results):
     return np.frombuffer(results.cpu().numpy().tobytes(), dtype=RESULT_DTYPE)
+
+
+def quantize_activations(x_bf16, a=None, a_scale=None):
+    """bf16 [M,K] -> (e4m3 bytes [M,K] uint8, fp32 power-of-two scales [M,K/128]); rule of
+    ds41_dense_quant (components/dense/src/dense.cu:8-16) with the group widened to 128."""
+    x_bf16 = _dev(x_bf16, torch.bfloat16, "x")
+    M, K = x_bf16.shape
+    if a is None:
+        a = torch.empty((M, K), dtype=torch.uint8, device=x_bf16.device)
+    if a_scale is None:
+        a_scale = torch.empty((M, K // 128), dtype=torch.float32, device=x_bf16.device)
+    with torch.cuda.device(x_bf16.device):
+        _check(lib().ds41_b200_quantize_activations(x_bf16.data_ptr(), a.data_ptr(), a_scale.data_ptr(), M, K, _stream()),
+               "ds41_b200_quantize_activations")
+    return a, a_scale
+
+
+def head_fp8(a, a_scale, w, w_scale, logits=None, error_flag=None):
+    """Block-scaled FP8 head GEMM: a uint8 [M,K] (e4m3), w uint8 [N,K] (e4m3) -> fp32 logits [M,N]."""
+    a = _dev(a, torch.uint8, "a"); w = _dev(w, torch.uint8, "w")
+    a_scale = _dev(a_scale, torch.float32, "a_scale"); w_scale = _dev(w_scale, torch.float32, "w_scale")
+    M, K = a.shape
+    N = w.shape[0]
+    if logits is None:
+        logits = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    with torch.cuda.device(a.device):
+        _check(lib().ds41_b200_head_fp8(a.data_ptr(), a_scale.data_ptr(), w.data_ptr(), w_scale.data_ptr(),
+                                        logits.data_ptr(), logits.stride(0), M, N, K,
+                                        error_flag.data_ptr() if error_flag is not None else None, _stream()),
+               "ds41_b200_head_fp8")
+    return logits
+
+
+def fuse_head_fp8_workspace_bytes(M, K):
+    return lib().ds41_fuse_head_fp8_workspace_bytes(M, K)
+
+
+def fuse_head_fp8(x_bf16, w, w_scale, logits=None, workspace=None, error_flag=None):
+    """x bf16 [M,K] -> fp32 logits [M,N]: activation quantisation + FP8 head in one call."""
+    x_bf16 = _dev(x_bf16, torch.bfloat16, "x"); w = _dev(w, torch.uint8, "w")
+    w_scale = _dev(w_scale, torch.float32, "w_scale")
+    M, K = x_bf16.shape
+    N = w.shape[0]
+    if logits is None:
+        logits = torch.empty((M, N), dtype=torch.float32, device=x_bf16.device)
+    if workspace is None:
+        workspace = torch.empty(fuse_head_fp8_workspace_bytes(M, K), dtype=torch.uint8, device=x_bf16.device)
+    with torch.cuda.device(x_bf16.device):
+        _check(lib().ds41_fuse_head_fp8(x_bf16.data_ptr(), w.data_ptr(), w_scale.data_ptr(), logits.data_ptr(), M, N, K,
+                                        workspace.data_ptr(), workspace.numel(),
+                                        error_flag.data_ptr() if error_flag is not None else None, _stream()),
+               "ds41_fuse_head_fp8")
+    return logits

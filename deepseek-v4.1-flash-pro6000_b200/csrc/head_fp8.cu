@@ -1,0 +1,405 @@
+// FP8 LM head for sm_100a: logits[m, n] = sum over 128-wide K blocks of a_scale[m, kb] * w_scale[n/128, kb] *
+// dot(a_e4m3[m, kb], w_e4m3[n, kb]).
+//
+// The reference's head is a BF16 GEMV (components/fuse-head/src/head_half_tune.cu:7-21) and its only FP8 GEMM is
+// ds41_dense_fp8 for the dense projections (components/dense/src/dense.cu:25-91, UE8M0 scales per 32x32 block).
+// This operator is new: e4m3 weights with one fp32 scale per 128x128 block, activations quantised per (row, 128-K
+// group) by the reference's power-of-two rule (dense.cu:8-16) widened to the weight block.  It keeps the plugin
+// conventions of fuse_head.h:8 (caller-owned buffers, stream-ordered, no allocation, no synchronisation).
+//
+// Kernel shape ("swap-AB" decode GEMM): the 128 vocabulary rows of a weight tile are the M dimension of
+// tcgen05.mma (one TMEM lane per vocabulary row) and the batch is its N dimension (16..128 TMEM columns), so a batch
+// of 1 wastes no tensor-core rows and the fp32 accumulators of one vocabulary row live in one thread of the
+// epilogue.  Per CTA: warp 0 streams W and A tiles with TMA (128-byte swizzle) into a ring of shared-memory stages,
+// warp 1 issues four K=32 tcgen05.mma per 128-wide K block into one of two TMEM accumulators, warps 2-5 pull each
+// finished K block out of TMEM (tcgen05.ld), apply the two scales in fp32 and keep the running sums in registers.
+// Every wait is bounded; on expiry the kernel raises *error_flag, frees its TMEM and returns.
+#include "ds41_b200.h"
+#include "host_error.h"
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ds41 {
+namespace {
+
+constexpr int kTileN = 128;   // vocabulary rows per tile (UMMA M)
+constexpr int kTileK = 128;   // K elements per block = one 128-byte swizzle row of e4m3
+constexpr int kThreadsHead = 192;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+struct Abort {  // shared flag: once set every later wait returns immediately
+  volatile int *flag;
+  __device__ __forceinline__ bool set() const { return *flag != 0; }
+};
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+// Bounded wait on a phase parity.  Returns false (and raises the abort flag) if the phase never completed.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, const Abort &ab) {
+  if (ab.set()) return false;
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(done)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((spin & 1023u) == 1023u && ab.set()) return false;
+  }
+  *ab.flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
+          "r"(smem_addr(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows are 128 bytes apart, groups of 8 rows 1024 bytes
+// apart (stride byte offset), leading byte offset unused (1), descriptor version 1 for sm_100.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= uint64_t((saddr & 0x3FFFFu) >> 4);        // start address, bits [0,14)
+  d |= uint64_t(1) << 16;                        // leading byte offset (>>4), bits [16,30)
+  d |= uint64_t(1024 >> 4) << 32;                // stride byte offset (>>4), bits [32,46)
+  d |= uint64_t(1) << 46;                        // version, bits [46,48)
+  d |= uint64_t(2) << 61;                        // layout type SWIZZLE_128B, bits [61,64)
+  return d;
+}
+// Instruction descriptor for kind::f8f6f4, E4M3 x E4M3 -> F32, both operands K-major, M=128, N=columns.
+__host__ __device__ constexpr uint32_t umma_idesc(int n_cols) {
+  return (1u << 4) | (uint32_t(n_cols >> 3) << 17) | (uint32_t(kTileN >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+template <int kCols>
+struct HeadSmem {
+  static constexpr int kStageBytes = kTileN * kTileK + kCols * kTileK;
+  static constexpr int kStages = (200 * 1024 - 32 * kCols * 4) / kStageBytes > 12 ? 12 : (200 * 1024 - 32 * kCols * 4) / kStageBytes;
+};
+
+struct HeadArgs {
+  const float *a_scale;  // [M, K/128]
+  const float *w_scale;  // [ceil(N/128), K/128]
+  float *logits;         // [M, ldl]
+  long long ldl;
+  int M, N, K;
+  int *error_flag;       // device word, raised on a wait timeout (may be null)
+};
+
+template <int kCols>
+__global__ void __launch_bounds__(kThreadsHead, 1)
+head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, HeadArgs p) {
+  constexpr int kStages = HeadSmem<kCols>::kStages;
+  constexpr int kStageBytes = HeadSmem<kCols>::kStageBytes;
+  constexpr uint32_t kTmemCols = 2 * kCols < 32 ? 32 : 2 * kCols;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  // carve: [stages][W tile 16 KB | A tile kCols*128 B], then the activation-scale table, then barriers
+  unsigned char *tiles = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~uintptr_t(1023));
+  float *sx = reinterpret_cast<float *>(tiles + size_t(kStages) * kStageBytes);  // [K/128][kCols]
+  const int kblocks = p.K / kTileK;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(sx + size_t(kblocks) * kCols);
+  uint64_t *full = bars, *empty = bars + kStages, *acc_full = bars + 2 * kStages, *acc_empty = bars + 2 * kStages + 2;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 4);
+  int *abort_word = reinterpret_cast<int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = (p.N + kTileN - 1) / kTileN, b_tiles = (p.M + kCols - 1) / kCols;
+  const int total_tiles = n_tiles * b_tiles;
+  Abort ab{abort_word};
+
+  if (threadIdx.x == 0) {
+    *abort_word = 0;
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // TMEM allocation by one full warp; the address lands in shared memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(kTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !ab.set(); tile += gridDim.x) {
+        const int nt = tile / b_tiles, bt = tile % b_tiles;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, ab)) break;
+          unsigned char *w_dst = tiles + size_t(stage) * kStageBytes, *a_dst = w_dst + kTileN * kTileK;
+          mbar_expect_tx(&full[stage], uint32_t(kStageBytes));
+          tma_load_2d(w_dst, &map_w, &full[stage], kb * kTileK, nt * kTileN);
+          tma_load_2d(a_dst, &map_a, &full[stage], kb * kTileK, bt * kCols);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (one lane)
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(kCols);
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !ab.set(); tile += gridDim.x) {
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, ab)) break;
+          if (!mbar_wait(&full[stage], phase, ab)) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t w_addr = smem_addr(tiles + size_t(stage) * kStageBytes), a_addr = w_addr + kTileN * kTileK;
+          const uint32_t d_addr = tmem_base + acc * kCols;
+#pragma unroll
+          for (int k = 0; k < kTileK / 32; ++k)
+            umma_f8(d_addr, umma_desc(w_addr + k * 32), umma_desc(a_addr + k * 32), idesc, k ? 1u : 0u);
+          umma_commit(&empty[stage]);    // stage may be refilled once these MMAs have read it
+          umma_commit(&acc_full[acc]);   // accumulator of this K block is complete
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue: 4 warps, one TMEM lane quadrant each
+    const int quad = warp & 3;                      // TMEM lanes [32*quad, 32*quad+32) are readable by this warp
+    const int et = threadIdx.x - 64;                // 0..127
+    uint32_t acc = 0, acc_phase = 0;
+    bool alive = true;  // warp-uniform; once false the remaining tiles are walked without waiting or computing,
+                        // so that all 128 epilogue threads still meet at every named barrier
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const int nt = tile / b_tiles, bt = tile % b_tiles;
+      // activation scales of this batch tile, transposed to [kb][column]
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // previous tile's readers are done with sx
+      for (int i = et; i < kblocks * kCols; i += 128) {
+        const int kb = i / kCols, col = i % kCols, m = bt * kCols + col;
+        sx[i] = m < p.M ? __ldg(p.a_scale + size_t(m) * kblocks + kb) : 0.f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      float sum[kCols];
+#pragma unroll
+      for (int c = 0; c < kCols; ++c) sum[c] = 0.f;
+      const float *wsc = p.w_scale + size_t(nt) * kblocks;
+      for (int kb = 0; kb < kblocks && alive; ++kb) {
+        alive = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], acc_phase, ab));
+        if (!alive) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const float sw = __ldg(wsc + kb);
+        const uint32_t taddr = tmem_base + acc * kCols + (uint32_t(quad * 32) << 16);
+        const float *sxk = sx + kb * kCols;
+        if constexpr (kCols == 16) {
+          uint32_t r[32];
+          tmem_ld16(taddr, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int c = 0; c < 16; ++c) sum[c] = fmaf(__uint_as_float(r[c]), sw * sxk[c], sum[c]);
+        } else {
+#pragma unroll
+          for (int c0 = 0; c0 < kCols; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(taddr + c0, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < 32; ++c) sum[c0 + c] = fmaf(__uint_as_float(r[c]), sw * sxk[c0 + c], sum[c0 + c]);
+          }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (alive) {
+        const int n = nt * kTileN + quad * 32 + lane;
+        if (n < p.N) {
+#pragma unroll
+          for (int c = 0; c < kCols; ++c) {
+            const int m = bt * kCols + c;
+            if (m < p.M) p.logits[size_t(m) * p.ldl + n] = sum[c];
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols));
+  }
+  if (threadIdx.x == 0 && *abort_word && p.error_flag) atomicExch(p.error_flag, 1);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Activation quantisation: per (row, 128-wide K group) scale = 2^ceil(log2(max(amax,1e-4)/448)), e4m3 round to
+// nearest even with saturation (components/dense/src/dense.cu:8-16 with the group widened from 32 to 128).
+__global__ void quantize_kernel(const __nv_bfloat16 *x, uint8_t *a, float *scale, int groups) {
+  const int g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (g >= groups) return;
+  const uint2 raw = *reinterpret_cast<const uint2 *>(x + size_t(g) * 128 + lane * 4);
+  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162 *>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162 *>(&raw.y);
+  float v[4] = {__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi)};
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+  for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const uint32_t bits = __float_as_uint(__fmul_rn(fmaxf(amax, 1e-4f), 1.f / 448.f));
+  const uint32_t exponent = (bits >> 23) + ((bits & 0x7fffffu) != 0);
+  const float s = __uint_as_float(exponent << 23);
+  uint32_t packed = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float q = fminf(448.f, fmaxf(-448.f, __fdiv_rn(v[i], s)));
+    packed |= uint32_t(__nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+  }
+  *reinterpret_cast<uint32_t *>(a + size_t(g) * 128 + lane * 4) = packed;
+  if (lane == 0) scale[g] = s;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                              const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn encoder() {
+  static EncodeFn fn = [] {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      sym = nullptr;
+    return reinterpret_cast<EncodeFn>(sym);
+  }();
+  return fn;
+}
+// 2-D uint8 tensor [rows, cols] row-major, box [box_rows, 128 bytes], 128-byte swizzle, zero fill outside.
+bool make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeFn enc = encoder();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols};
+  const cuuint32_t box[2] = {uint32_t(kTileK), box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int kCols>
+cudaError_t launch_head(const CUtensorMap &mw, const CUtensorMap &ma, const HeadArgs &p, int sms, cudaStream_t stream) {
+  constexpr int kStages = HeadSmem<kCols>::kStages;
+  const size_t smem = 1024 + size_t(kStages) * HeadSmem<kCols>::kStageBytes + size_t(p.K / kTileK) * kCols * 4 +
+                      (2 * kStages + 4) * 8 + 16;
+  static thread_local int configured = -1;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (configured != dev) {
+    e = cudaFuncSetAttribute(head_fp8_kernel<kCols>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    configured = dev;
+  }
+  if (smem > 227 * 1024) return cudaErrorInvalidValue;
+  const int tiles = ((p.N + kTileN - 1) / kTileN) * ((p.M + kCols - 1) / kCols);
+  head_fp8_kernel<kCols><<<tiles < sms ? tiles : sms, kThreadsHead, smem, stream>>>(mw, ma, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+}  // namespace ds41
+
+using namespace ds41;
+
+extern "C" int ds41_b200_quantize_activations(const void *x_bf16, void *a_e4m3, float *a_scale, int M, int K,
+                                              cudaStream_t stream) {
+  if (!x_bf16 || !a_e4m3 || !a_scale || M < 1 || K < 128 || K % 128) return invalid("quantize arguments");
+  const int groups = M * (K / 128);
+  quantize_kernel<<<(groups * 32 + 255) / 256, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(x_bf16),
+                                                                 static_cast<uint8_t *>(a_e4m3), a_scale, groups);
+  return int(cudaGetLastError());
+}
+
+extern "C" int ds41_b200_head_fp8(const void *a_e4m3, const float *a_scale, const void *w_e4m3, const float *w_scale,
+                                  float *logits, int64_t logits_stride, int M, int N, int K, int *error_flag,
+                                  cudaStream_t stream) {
+  if (!a_e4m3 || !a_scale || !w_e4m3 || !w_scale || !logits || M < 1 || N < 1 || K < 128 || K % 128 || K > 16384 ||
+      logits_stride < N)
+    return invalid("head arguments");
+  if ((reinterpret_cast<uintptr_t>(a_e4m3) & 15u) || (reinterpret_cast<uintptr_t>(w_e4m3) & 15u))
+    return invalid("head operands must be 16-byte aligned");
+  int dev = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return int(e);
+  const int cols = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+  CUtensorMap mw, ma;
+  if (!make_map(&mw, w_e4m3, uint64_t(N), uint64_t(K), kTileN) || !make_map(&ma, a_e4m3, uint64_t(M), uint64_t(K), uint32_t(cols)))
+    return invalid("cuTensorMapEncodeTiled failed");
+  HeadArgs p{a_scale, w_scale, logits, logits_stride, M, N, K, error_flag};
+  switch (cols) {
+    case 16: e = launch_head<16>(mw, ma, p, sms, stream); break;
+    case 32: e = launch_head<32>(mw, ma, p, sms, stream); break;
+    case 64: e = launch_head<64>(mw, ma, p, sms, stream); break;
+    default: e = launch_head<128>(mw, ma, p, sms, stream); break;
+  }
+  return int(e);
+}
+
+extern "C" size_t ds41_fuse_head_fp8_workspace_bytes(int M, int K) {
+  if (M < 1 || K < 128 || K % 128) return 0;
+  return ((size_t(M) * K + 255) & ~size_t(255)) + size_t(M) * (K / 128) * sizeof(float);
+}
+
+extern "C" int ds41_fuse_head_fp8(const void *x_bf16, const void *w_e4m3, const float *w_scale, float *logits, int M,
+                                  int N, int K, void *workspace, size_t workspace_bytes, int *error_flag,
+                                  cudaStream_t stream) {
+  const size_t need = ds41_fuse_head_fp8_workspace_bytes(M, K);
+  if (!need || !workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+    return invalid("head workspace too small or misaligned");
+  uint8_t *a = static_cast<uint8_t *>(workspace);
+  float *a_scale = reinterpret_cast<float *>(a + ((size_t(M) * K + 255) & ~size_t(255)));
+  int rc = ds41_b200_quantize_activations(x_bf16, a, a_scale, M, K, stream);
+  if (rc) return rc;
+  return ds41_b200_head_fp8(a, a_scale, w_e4m3, w_scale, logits, N, M, N, K, error_flag, stream);
+}

@@ -51,6 +51,26 @@ uint32_t ds41_spark_rng_word_v2(uint64_t seed, uint64_t step, uint32_t slot, uin
 double ds41_spark_uniform_v2(uint64_t seed, uint64_t step, uint32_t slot, uint32_t purpose, uint64_t draw);
 const char *ds41_spark_error(void);
 
+/* ---- LM head -------------------------------------------------------------------------------------------
+ * FP8 head: logits[m,n] = sum over 128-wide K blocks kb of a_scale[m,kb] * w_scale[n/128,kb] *
+ * dot(a[m,kb], w[n,kb]) with e4m3 operands and fp32 output.  There is no FP8 head in the reference; the entry
+ * points keep the call shape of ds41_fuse_head_decode (components/fuse-head/include/ds41/fuse_head.h:9-10:
+ * activations, weights, fp32 logits [M,N], M, N, K, stream) and the two-step quantise / multiply split of
+ * ds41_dense_quant + ds41_dense_fp8 (components/dense/include/ds41/dense.h:10-13; dense.cu:8-16,25-91).
+ *   w_e4m3  [N,K] row-major, K % 128 == 0;  w_scale [ceil(N/128), K/128] fp32
+ *   a_e4m3  [M,K];  a_scale [M, K/128] fp32 (powers of two, as ds41_dense_quant produces them, group 128)
+ *   error_flag: optional device int raised to 1 if a bounded device-side wait expired (logits then invalid). */
+int ds41_b200_quantize_activations(const void *x_bf16, void *a_e4m3, float *a_scale, int M, int K,
+                                   cudaStream_t stream);
+int ds41_b200_head_fp8(const void *a_e4m3, const float *a_scale, const void *w_e4m3, const float *w_scale,
+                       float *logits, int64_t logits_stride, int M, int N, int K, int *error_flag,
+                       cudaStream_t stream);
+/* Quantise + multiply in one call: x_bf16 [M,K] -> logits fp32 [M,N] (stride N).  workspace: caller-owned device
+ * memory of ds41_fuse_head_fp8_workspace_bytes(M,K) bytes, 256-byte aligned. */
+size_t ds41_fuse_head_fp8_workspace_bytes(int M, int K);
+int ds41_fuse_head_fp8(const void *x_bf16, const void *w_e4m3, const float *w_scale, float *logits, int M, int N,
+                       int K, void *workspace, size_t workspace_bytes, int *error_flag, cudaStream_t stream);
+
 /* ---- sampler: logits -> token ids -----------------------------------------------------------------------
  * Replaces, fused and batched on the device, the engine's per-token host sequence
  *   probabilities(logits, T, top_p)  (engine/src/sampling.cpp:205-219 -> spark sampling.cpp:30-38)
