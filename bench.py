@@ -1,0 +1,516 @@
+#!/usr/bin/env python
+"""Benchmark of the decode-tail hot path (FP8 LM head -> fused sampler -> MTP verify) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One "step" is one pass of the hot path over one batch of synthetic input (BASELINE.json `configs`):
+  cfg2_b{1,8,64}  hidden bf16 [B,4096] -> activation quantiser -> FP8 head [129280,4096] -> top-p sampler (T=0.6, p=0.95)
+  cfg3_verify     32 sequences x (1 target + 2 draft) logits rows -> accept / residual / bonus
+  cfg4_penalties  256 rows: 32K-token history penalties + bitmask + top-k 50 + top-p 0.9, T=0.8
+  cfg5_b1024      B=1024, FP8 head + sampler; with --gpus N>1 the vocabulary is sharded over the ranks
+Default: cfg2_b64 on one GPU, cfg5_b1024 (vocabulary sharded, one NCCL all-gather per step) on several.
+Prints ONE JSON line (rank 0).  Weights stay resident in HBM (as in the reference engine); `value` is measured with the
+step's inputs already on the device, `e2e` with the hidden states copied from pinned host memory and the token ids
+read back every step.  `--impl reference` times the reference's own CPU sampling rule on the host cores.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+VOCAB, HIDDEN = 129280, 4096
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised
+# under profiles/ (None = not captured yet)
+NCU_TRAFFIC = {}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) >= 9:
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------- our arm
+def make_weights(torch, device, rows, seed):
+    """e4m3 weights ~ quantise(N(0, 0.02^2)) with one fp32 scale per 128x128 block (BASELINE config 2)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    wq = torch.empty((rows, HIDDEN), dtype=torch.uint8, device=device)
+    ws = torch.empty(((rows + 127) // 128, HIDDEN // 128), dtype=torch.float32, device=device)
+    chunk = 128 * 64
+    for r0 in range(0, rows, chunk):
+        r1 = min(rows, r0 + chunk)
+        w = torch.randn(r1 - r0, HIDDEN, device=device, generator=g) * 0.02
+        pad = (-w.shape[0]) % 128
+        if pad:
+            w = torch.cat([w, torch.zeros(pad, HIDDEN, device=device)])
+        blocks = w.view(-1, 128, HIDDEN // 128, 128)
+        s = (blocks.abs().amax(dim=(1, 3)) / 448.0).clamp_min(1e-30)
+        q = (blocks / s[:, None, :, None]).reshape(-1, HIDDEN).to(torch.float8_e4m3fn).view(torch.uint8)
+        wq[r0:r1] = q[: r1 - r0]
+        ws[r0 // 128:(r1 + 127) // 128] = s
+    return wq, ws
+
+
+def zipf_gauss_logits(torch, device, rows, seed, sigma=3.0):
+    g = torch.Generator(device=device).manual_seed(seed)
+    base = -1.1 * torch.log(torch.arange(1, VOCAB + 1, device=device, dtype=torch.float32))
+    out = torch.empty((rows, VOCAB), device=device)
+    for r in range(rows):
+        out[r] = base[torch.randperm(VOCAB, device=device, generator=g)]
+    out += sigma * torch.randn(rows, VOCAB, device=device, generator=g)
+    return out
+
+
+class HeadSample:
+    """cfg2 / cfg5: hidden -> quantise -> FP8 head (this rank's vocabulary slice) -> sampler."""
+
+    def __init__(self, pkg, torch, device, batch, rank, world, temperature=0.6, top_p=0.95):
+        self.pkg, self.torch, self.device, self.B, self.rank, self.world = pkg, torch, device, batch, rank, world
+        self.t, self.top_p = temperature, top_p
+        blocks = VOCAB // 128
+        per, extra = divmod(blocks, world)
+        counts = [per + (1 if r < extra else 0) for r in range(world)]
+        self.v0 = 128 * sum(counts[:rank])
+        self.vn = 128 * counts[rank]
+        self.wq, self.ws = make_weights(torch, device, self.vn, 1234 + rank)
+        g = torch.Generator(device=device).manual_seed(99)
+        self.ring = [torch.randn(batch, HIDDEN, device=device, generator=g).to(torch.bfloat16) for _ in range(16)]
+        self.host_ring = [h.cpu().pin_memory() for h in self.ring]
+        self.hidden = torch.empty_like(self.ring[0])
+        self.a = torch.empty((batch, HIDDEN), dtype=torch.uint8, device=device)
+        self.a_scale = torch.empty((batch, HIDDEN // 128), dtype=torch.float32, device=device)
+        self.logits = torch.empty((batch, self.vn), dtype=torch.float32, device=device)
+        self.seeds = torch.arange(batch, dtype=torch.int64, device=device) + 17
+        self.steps = torch.zeros(batch, dtype=torch.int64, device=device)
+        self.tokens = torch.empty(batch, dtype=torch.int32, device=device)
+        self.status = torch.empty(batch, dtype=torch.int32, device=device)
+        self.tokens_host = torch.empty(batch, dtype=torch.int32).pin_memory()
+        self.flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self.units = batch
+        self.launches_per_step = 3
+        self.h2d, self.d2h = batch * HIDDEN * 2, batch * 4
+        self.kernel = "head_fp8_kernel"
+        self.alg_bytes = self.vn * HIDDEN + self.ws.numel() * 4 + batch * HIDDEN + batch * 32 * 4
+        self.alg_flops = 2.0 * batch * self.vn * HIDDEN
+        self.bound = "hbm" if batch <= 128 else "tensor"
+        self.sharded = None
+        if world > 1:
+            from importlib import import_module
+            self.sharded = import_module("ds41_b200.sharded").ShardedSampler(pkg, torch, device, batch, self.v0, self.vn,
+                                                                           VOCAB, temperature, top_p)
+            self.launches_per_step = 2 + self.sharded.launches_per_step
+
+    def step(self, i, hidden=None, ev=None):
+        pkg = self.pkg
+        x = self.ring[i % len(self.ring)] if hidden is None else hidden
+        self.steps.add_(1)  # a fresh Philox step per decode step (spark.h:122-128)
+        pkg.quantize_activations(x, self.a, self.a_scale)
+        if ev:
+            ev[0].record()
+        pkg.head_fp8(self.a, self.a_scale, self.wq, self.ws, self.logits, self.flag)
+        if ev:
+            ev[1].record()
+        if self.sharded:
+            self.sharded.sample(self.logits, self.seeds, self.steps, self.tokens, self.status)
+        else:
+            pkg.sample_logits(self.logits, self.t, self.top_p, self.seeds, self.steps, tokens=self.tokens, status=self.status)
+
+    def e2e_step(self, i):
+        self.hidden.copy_(self.host_ring[i % len(self.host_ring)], non_blocking=True)
+        self.step(i, self.hidden)
+        self.tokens_host.copy_(self.tokens, non_blocking=True)
+        self.torch.cuda.current_stream().synchronize()
+        return self.tokens_host
+
+    def check(self):
+        assert self.flag.item() == 0, "head kernel reported a wait timeout"
+        st = self.status.cpu().numpy()
+        assert (st >= 0).all(), st
+
+
+class VerifyWorkload:
+    """cfg3: 32 sequences x (1 target + 2 draft) positions, V=129280."""
+
+    def __init__(self, pkg, torch, device, seqs=32, drafts=2, temperature=0.6, top_p=0.95, sigma=0.35):
+        self.pkg, self.torch, self.device = pkg, torch, device
+        self.seqs, self.drafts, self.t, self.top_p = seqs, drafts, temperature, top_p
+        self.sets = []
+        for k in range(3):  # three input sets (3 x 83 MB > L2) cycled between steps
+            target = zipf_gauss_logits(torch, device, seqs * (drafts + 1), 100 + k)
+            base = target.view(seqs, drafts + 1, VOCAB)[:, :drafts].reshape(-1, VOCAB)
+            draft = base + sigma * torch.randn(base.shape, device=device)
+            seeds = torch.arange(seqs, dtype=torch.int64, device=device) + 5
+            steps = torch.full((seqs,), 1000 + k, dtype=torch.int64, device=device)
+            ids = torch.empty(seqs * drafts, dtype=torch.int32, device=device)
+            for d in range(drafts):  # proposals drawn from q at (seed, step, slot=d, Draft)
+                tok, _ = pkg.sample_logits(draft[d::drafts], temperature, top_p, seeds, steps, slot=d, purpose=1)
+                ids[d::drafts] = tok
+            self.sets.append((target, draft.contiguous(), ids, seeds, steps))
+        self.scratch = torch.empty(pkg.verify_scratch_bytes(seqs, drafts), dtype=torch.uint8, device=device)
+        self.results = torch.empty(seqs * 40, dtype=torch.uint8, device=device)
+        self.status = torch.empty(seqs, dtype=torch.int32, device=device)
+        self.results_host = torch.empty(seqs * 40, dtype=torch.uint8).pin_memory()
+        self.host_sets = None
+        self.units = seqs  # one verified transaction per sequence; emitted tokens are reported separately
+        self.launches_per_step = 3
+        self.h2d = (seqs * (2 * drafts + 1)) * VOCAB * 4 + seqs * drafts * 4
+        self.d2h = seqs * 40
+        self.kernel = "row_kernel"
+        self.alg_bytes = seqs * (2 * drafts + 1) * VOCAB * 4
+        self.alg_flops = 0.0
+        self.bound = "hbm"
+
+    def step(self, i, inputs=None, ev=None):
+        target, draft, ids, seeds, steps = inputs or self.sets[i % len(self.sets)]
+        if ev:
+            ev[0].record()
+        self.pkg.verify_logits(target, draft, ids, self.drafts, self.t, self.top_p, seeds, steps, self.scratch,
+                               self.results, self.status)
+        if ev:
+            ev[1].record()
+
+    def e2e_step(self, i):
+        torch = self.torch
+        if self.host_sets is None:
+            self.host_sets = [tuple(t.cpu().pin_memory() for t in s[:3]) for s in self.sets]
+            self.dev_in = tuple(torch.empty_like(t) for t in self.sets[0][:3])
+        for d, h in zip(self.dev_in, self.host_sets[i % len(self.host_sets)]):
+            d.copy_(h, non_blocking=True)
+        s = self.sets[i % len(self.sets)]
+        self.step(i, self.dev_in + (s[3], s[4]))
+        self.results_host.copy_(self.results, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.results_host
+
+    def check(self):
+        assert (self.status.cpu().numpy() >= 0).all()
+
+
+class PenaltyWorkload:
+    """cfg4: 256 rows, 32K-token histories, bitmask with 1-5% of ids allowed, top-k 50 then top-p 0.9, T=0.8."""
+
+    def __init__(self, pkg, torch, device, batch=256):
+        self.pkg, self.torch, self.device, self.B = pkg, torch, device, batch
+        g = torch.Generator(device=device).manual_seed(5)
+        self.logits = zipf_gauss_logits(torch, device, batch, 41)
+        zipf = 1.0 / torch.arange(1, VOCAB + 1, device=device, dtype=torch.float64) ** 1.1
+        self.history = torch.empty((batch, 32768), dtype=torch.int32, device=device)
+        for r in range(batch):
+            perm = torch.randperm(VOCAB, device=device, generator=g)
+            self.history[r] = perm[torch.multinomial(zipf, 32768, replacement=True, generator=g)].int()
+        mask = torch.zeros((batch, VOCAB), dtype=torch.bool, device=device)
+        for r in range(batch):
+            want = int((0.01 + 0.04 * ((r * 37) % 100) / 100.0) * VOCAB)
+            starts = torch.randint(0, VOCAB - 300, (max(1, want // 136),), device=device, generator=g)
+            lens = torch.randint(8, 264, starts.shape, device=device, generator=g)
+            for s0, l0 in zip(starts.tolist(), lens.tolist()):
+                mask[r, s0:s0 + l0] = True
+        words = (mask.view(batch, VOCAB // 32, 32).long() << torch.arange(32, device=device)).sum(-1)
+        self.mask = torch.where(words >= 2 ** 31, words - 2 ** 32, words).to(torch.int32)  # uint32 bit patterns
+        self.seeds = torch.arange(batch, dtype=torch.int64, device=device)
+        self.steps = torch.zeros(batch, dtype=torch.int64, device=device)
+        self.tokens = torch.empty(batch, dtype=torch.int32, device=device)
+        self.status = torch.empty(batch, dtype=torch.int32, device=device)
+        self.tokens_host = torch.empty(batch, dtype=torch.int32).pin_memory()
+        self.host = None
+        self.units = batch
+        self.launches_per_step = 1
+        self.h2d = batch * (VOCAB * 4 + 32768 * 4 + VOCAB // 8)
+        self.d2h = batch * 4
+        self.kernel = "row_kernel"
+        self.alg_bytes = batch * (VOCAB * 4 + 32768 * 4 + VOCAB // 8)
+        self.alg_flops = 0.0
+        self.bound = "hbm"
+
+    def step(self, i, inputs=None, ev=None):
+        logits, history, mask = inputs or (self.logits, self.history, self.mask)
+        self.steps.add_(1)
+        if ev:
+            ev[0].record()
+        self.pkg.sample_logits(logits, 0.8, 0.9, self.seeds, self.steps, top_k=50, history=history, repetition=1.1,
+                               presence=0.3, frequency=0.2, mask=mask, tokens=self.tokens, status=self.status)
+        if ev:
+            ev[1].record()
+
+    def e2e_step(self, i):
+        torch = self.torch
+        if self.host is None:
+            self.host = tuple(t.cpu().pin_memory() for t in (self.logits, self.history, self.mask))
+            self.dev_in = tuple(torch.empty_like(t) for t in (self.logits, self.history, self.mask))
+        for d, h in zip(self.dev_in, self.host):
+            d.copy_(h, non_blocking=True)
+        self.step(i, self.dev_in)
+        self.tokens_host.copy_(self.tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.tokens_host
+
+    def check(self):
+        assert (self.status.cpu().numpy() >= 0).all()
+
+
+def cpu_baseline(workload_name, budget_rows=None):
+    """Times the reference's own host sampling rule (oracle/_ref when it was compiled here, else this repository's
+    port) on the host cores: a bounded sample of the workload's logits rows, one row per thread at a time."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle_lib
+    from concurrent.futures import ThreadPoolExecutor
+    orc = oracle_lib.Oracle()
+    ref = oracle_lib.Reference()
+    cores = os.cpu_count() or 1
+    if workload_name.startswith("cfg3"):
+        seqs = min(32, max(cores, 8))
+        target = orc.gen_logits(3, seqs * 3, VOCAB)
+        draft = orc.gen_perturbed(3, target.reshape(seqs, 3, VOCAB)[:, :2].reshape(-1, VOCAB), 0.35)
+        seeds, steps = np.arange(seqs, dtype=np.uint64), np.full(seqs, 9, np.uint64)
+        ids = np.zeros((seqs, 2), np.int32)
+        for k in range(2):
+            ids[:, k], _ = orc.sample_rows(draft[k::2], 0.6, 0.95, seeds, steps, slot=k, purpose=1, threads=cores)
+        t0 = time.perf_counter()
+        if ref.available:
+            def one(s):
+                p = np.stack([ref.probabilities(target[s * 3 + k], 0.6, 0.95) for k in range(3)])
+                q = np.stack([ref.probabilities(draft[s * 2 + k], 0.6, 0.95) for k in range(2)])
+                return ref.reject_sample(ids[s], q, p, int(seeds[s]), int(steps[s]), 0.6)
+            with ThreadPoolExecutor(cores) as ex:
+                list(ex.map(one, range(seqs)))
+            kind = "reference"
+        else:
+            orc.verify_rows(target, draft, ids, 2, 0.6, 0.95, seeds, steps, threads=cores)
+            kind = "port"
+        dt = time.perf_counter() - t0
+        return {"value": seqs / dt, "unit": "sequences/s", "cores": cores, "kind": kind,
+                "sample": f"{seqs} transactions x (3 target + 2 draft) rows, probabilities_rows + reject_sample"}
+    if workload_name.startswith("cfg4"):
+        rows = min(256, 2 * cores)
+        x = orc.gen_logits(4, rows, VOCAB)
+        hist = orc.gen_history(4, rows, VOCAB, 32768)
+        mask = orc.gen_mask(4, rows, VOCAB)
+        t0 = time.perf_counter()
+        orc.sample_rows(x, 0.8, 0.9, np.arange(rows), np.arange(rows), top_k=50, history=hist, repetition=1.1,
+                        presence=0.3, frequency=0.2, mask=mask, threads=cores)
+        dt = time.perf_counter() - t0
+        return {"value": rows / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
+                "sample": f"{rows} rows; penalties/bitmask/top-k have no reference code, so this is the repository's CPU rule"}
+    rows = budget_rows or max(64, 4 * cores)
+    x = orc.gen_logits(2, min(rows, 64), VOCAB)
+    x = np.concatenate([x] * ((rows + x.shape[0] - 1) // x.shape[0]))[:rows]
+    t0 = time.perf_counter()
+    if ref.available:
+        def one(r):
+            return ref.sample(ref.probabilities(x[r], 0.6, 0.95), r, 1, 0, 0)
+        with ThreadPoolExecutor(cores) as ex:
+            list(ex.map(one, range(rows)))
+        kind = "reference"
+    else:
+        orc.sample_rows(x, 0.6, 0.95, np.arange(rows), np.ones(rows), threads=cores)
+        kind = "port"
+    dt = time.perf_counter() - t0
+    return {"value": rows / dt, "unit": "tokens/s", "cores": cores, "kind": kind,
+            "sample": f"{rows} logits rows [129280] through probabilities(T=0.6, top_p=0.95) + sample; the reference has "
+                      "no CPU LM head, so the head is not in this figure"}
+
+
+def workload_config(name, world):
+    cfg = {"workload": name, "vocab": VOCAB, "data_recipe": "BASELINE.json configs, seeded synthetic"}
+    if name.startswith("cfg2") or name.startswith("cfg5"):
+        cfg.update({"hidden": HIDDEN, "batch": int(name.split("_b")[1]), "temperature": 0.6, "top_p": 0.95,
+                    "weights": "e4m3 [129280,4096] + fp32 scale per 128x128, resident in HBM",
+                    "parallelism": "1 GPU" if world == 1 else f"vocab-sharded x{world} (128-row blocks), 1 NCCL all-gather/step",
+                    "l2": "529.5 MB of weights stream from HBM every step (> 126 MB L2); hidden states cycle over 16 buffers"})
+    elif name.startswith("cfg3"):
+        cfg.update({"sequences": 32, "drafts": 2, "temperature": 0.6, "top_p": 0.95,
+                    "l2": "three 83 MB input sets cycled, so every step reads logits from HBM"})
+    elif name.startswith("cfg4"):
+        cfg.update({"batch": 256, "history": 32768, "top_k": 50, "top_p": 0.9, "temperature": 0.8,
+                    "l2": "170 MB of inputs per step (> 126 MB L2)"})
+    return cfg
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    name = args.workload
+    samples = []
+    for _ in range(args.warmup if args.warmup < 2 else 1):
+        cpu_baseline(name)
+    t_all = time.perf_counter()
+    base = None
+    for _ in range(max(1, min(args.steps, 5))):
+        base = cpu_baseline(name)
+        samples.append(base["value"])
+        if time.perf_counter() - t_all > 120:
+            break
+    value = statistics.median(samples)
+    base["value"] = value
+    line = {"impl": "reference", "metric": metric_name(name), "value": value, "unit": base["unit"], "n_gpus": args.gpus,
+            "steps": len(samples), "warmup": 1, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f64", "data": "synthetic", "config": workload_config(name, 1),
+            "cpu_baseline": base, "e2e": {"value": value, "unit": base["unit"], "h2d_bytes_per_step": 0,
+                                          "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def metric_name(name):
+    return "verified_sequences_per_s" if name.startswith("cfg3") else "sampled_tokens_per_s"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default=None)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.workload is None:
+        args.workload = "cfg2_b64" if max(world, args.gpus) == 1 else "cfg5_b1024"
+    if args.impl == "reference":
+        return run_reference(args, rank, world)
+
+    import torch
+    import __graft_entry__ as entry
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    pkg = entry.load_package()
+    name = args.workload
+    if name.startswith("cfg2") or name.startswith("cfg5"):
+        wl = HeadSample(pkg, torch, device, int(name.split("_b")[1]), rank, world)
+    elif name.startswith("cfg3"):
+        wl = VerifyWorkload(pkg, torch, device)
+    elif name.startswith("cfg4"):
+        wl = PenaltyWorkload(pkg, torch, device)
+    else:
+        raise SystemExit(f"unknown workload {name}")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    warm = max(3, args.warmup)
+    for i in range(warm):
+        wl.step(i)
+    barrier()
+    wl.check()
+    # ---- device-resident timing: K steps between two events, plus an event pair around the dominant kernel
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    clocks = ClockSampler(local)
+    if rank == 0:
+        clocks.start()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for i in range(args.steps):
+        wl.step(i, ev=pairs[i])
+    t1.record()
+    barrier()
+    ms = t0.elapsed_time(t1)
+    kernel_ms = sum(a.elapsed_time(b) for a, b in pairs) / args.steps
+    # ---- end to end: inputs from pinned host memory, result read back every step
+    e2e_steps = args.steps
+    for i in range(3):
+        wl.e2e_step(i)
+    barrier()
+    w0 = time.perf_counter()
+    for i in range(e2e_steps):
+        wl.e2e_step(i)
+    barrier()
+    e2e_s = time.perf_counter() - w0
+    clock_info = clocks.stop() if rank == 0 else None
+    wl.check()
+    if world > 1:
+        t = torch.tensor([ms, e2e_s, kernel_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s, kernel_ms = t.tolist()
+    if rank == 0:
+        pk = peaks()
+        units = wl.units
+        if wl.bound == "hbm":
+            achieved = wl.alg_bytes / (kernel_ms * 1e-3) / 1e9
+            roof = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / pk["hbm_gbs"]}
+        else:
+            achieved = wl.alg_flops / (kernel_ms * 1e-3) / 1e12
+            roof = {"bound": "tensor", "achieved": achieved, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / pk["bf16_tflops"]}
+        roof.update({"traffic": NCU_TRAFFIC.get(name), "kernel": wl.kernel, "kernel_ms": kernel_ms,
+                     "peak_source": pk["source"], "algorithmic_per_launch": wl.alg_bytes if wl.bound == "hbm" else wl.alg_flops})
+        line = {"metric": metric_name(name), "value": units * args.steps / (ms * 1e-3),
+                "unit": "sequences/s" if name.startswith("cfg3") else "tokens/s", "n_gpus": world, "steps": args.steps,
+                "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True,
+                "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+                "dtype": "e4m3 x e4m3 -> f32 (head), f32 logits / f64 sampler" if hasattr(wl, "wq") else "f32 logits, f64 sums",
+                "data": "synthetic", "config": workload_config(name, world), "clocks": clock_info,
+                "e2e": {"value": units * e2e_steps / e2e_s, "unit": "sequences/s" if name.startswith("cfg3") else "tokens/s",
+                        "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_s / e2e_steps * 1e3},
+                "gpu_launches": wl.launches_per_step * args.steps, "roofline": roof}
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = cpu_baseline(name)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
