@@ -71,6 +71,8 @@ def lib():
         L.ds41_spark_uniform_v2.argtypes = [_u64, _u64, _u32, _u32, _u64]
         L.ds41_b200_sample_logits.argtypes = [C.POINTER(SampleArgs), _P]
         L.ds41_b200_verify_logits.argtypes = [C.POINTER(VerifyArgs), _P]
+        L.ds41_b200_verify_logits_static.argtypes = [C.POINTER(VerifyArgs), _P]
+        L.ds41_b200_verify_logits_static_max_rows.restype = C.c_int
         L.ds41_b200_quantize_activations.argtypes = [_P, _P, _P, C.c_int, C.c_int, _P]
         L.ds41_b200_head_fp8.argtypes = [_P, _P, _P, _P, _P, _i64, C.c_int, C.c_int, C.c_int, _P, _P]
         L.ds41_fuse_head_fp8_workspace_bytes.restype = C.c_size_t

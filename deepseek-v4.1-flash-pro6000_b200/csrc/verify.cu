@@ -179,3 +179,60 @@ extern "C" int ds41_b200_verify_logits(const ds41_b200_verify_args *p, cudaStrea
   cfg.attrs = attr; cfg.numAttrs = 1;
   return int(cudaLaunchKernelEx(&cfg, verify_kernel, v));
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Verification without any caller-provided or library-allocated scratch.
+//
+// Some hosts of this library may not allocate device memory at the point where they verify a speculative step: an
+// engine that has handed all of its HBM to weight / KV / expert pools at start-up and runs with a fixed memory plan,
+// or a plugin loaded into a process whose allocator it must not touch.  For them the row statistics live in a
+// fixed-size array that is part of the library image itself, so the call needs nothing but the inputs and outputs.
+//
+// The array is device memory reserved on EVERY GPU that loads the library, from load until the process exits
+// (kStaticStatRows * sizeof(RowStats) = 48 KiB).  Its name is only a host-side handle: the address the kernels need
+// is looked up once per device with cudaGetSymbolAddress, with that device current, on the first call made for the
+// device.  That first call therefore does a little set-up work (it may load the module) and should be made before
+// any stream capture begins; later calls only enqueue kernels.  No cudaMalloc / cudaFree or allocating library
+// routine is ever called on this path.
+//
+// All calls share the one array.  Every record a call reads is written earlier by that same call (the statistics
+// kernels fill all sequences*(2*drafts+1) records before the per-sequence kernel starts), so nothing has to be
+// cleared between calls and stale contents of a previous, larger call are never read.  Two calls that overlap on
+// the GPU (different streams, or different host threads without ordering) would overwrite each other's records:
+// the caller must serialise them, as the reference requires for its own sampler object (spark.h:35-36).
+namespace ds41 {
+namespace {
+constexpr int kStaticStatRows = 1024;  // sequences * (2*drafts + 1) may not exceed this
+static __device__ __align__(256) unsigned char g_static_stats[kStaticStatRows * sizeof(RowStats)];
+constexpr int kMaxDevices = 64;
+void *g_static_stats_addr[kMaxDevices] = {};
+}  // namespace
+}  // namespace ds41
+
+extern "C" int ds41_b200_verify_logits_static_max_rows(void) { return ds41::kStaticStatRows; }
+
+extern "C" int ds41_b200_verify_logits_static(const ds41_b200_verify_args *p, cudaStream_t stream) {
+  using namespace ds41;
+  if (!p || p->struct_bytes != sizeof(ds41_b200_verify_args)) return invalid("verify args: struct size / ABI mismatch");
+  if (p->sequences < 1 || p->drafts < 0 || p->drafts > 5) return invalid("verify arguments");
+  const long long rows = (long long)p->sequences * (2 * p->drafts + 1);
+  if (rows > kStaticStatRows)
+    return invalid("ds41_b200_verify_logits_static: sequences*(2*drafts+1) exceeds the built-in limit of 1024 "
+                   "statistics records; use ds41_b200_verify_logits with caller scratch");
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return int(e);
+  if (dev < 0 || dev >= kMaxDevices) return invalid("device ordinal beyond the static scratch table");
+  void *addr = g_static_stats_addr[dev];
+  if (!addr) {  // first call on this device: resolve the device address of the array (idempotent, so a race between
+                // two first calls only repeats the lookup)
+    e = cudaGetSymbolAddress(&addr, g_static_stats);
+    if (e != cudaSuccess) return int(e);
+    if (!addr) return invalid("cudaGetSymbolAddress returned a null address");
+    g_static_stats_addr[dev] = addr;
+  }
+  ds41_b200_verify_args with_scratch = *p;
+  with_scratch.scratch = addr;
+  with_scratch.scratch_bytes = sizeof(g_static_stats);
+  return ds41_b200_verify_logits(&with_scratch, stream);
+}

@@ -126,6 +126,16 @@ typedef struct ds41_b200_verify_args {
 size_t ds41_b200_verify_scratch_bytes(int sequences, int drafts);
 int ds41_b200_verify_logits(const ds41_b200_verify_args *args, cudaStream_t stream);
 
+/* Same verification for callers that cannot provide or allocate scratch memory (an engine running on a fixed
+ * device-memory plan, a plugin that must not touch its host's allocator).  This entry point has no counterpart in
+ * the reference.  args->scratch and args->scratch_bytes are ignored: the per-row statistics live in a 48 KiB device
+ * array built into the library, so sequences*(2*drafts+1) may not exceed
+ * ds41_b200_verify_logits_static_max_rows() (1024); larger requests return cudaErrorInvalidValue with a message.
+ * The first call on each device looks up the array's address (make it before any stream capture); no call
+ * allocates.  All calls share the array, so calls that could overlap on the GPU must be serialised by the caller. */
+int ds41_b200_verify_logits_static_max_rows(void);
+int ds41_b200_verify_logits_static(const ds41_b200_verify_args *args, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
