@@ -119,11 +119,8 @@ class HeadSample:
     def __init__(self, pkg, torch, device, batch, rank, world, temperature=0.6, top_p=0.95):
         self.pkg, self.torch, self.device, self.B, self.rank, self.world = pkg, torch, device, batch, rank, world
         self.t, self.top_p = temperature, top_p
-        blocks = VOCAB // 128
-        per, extra = divmod(blocks, world)
-        counts = [per + (1 if r < extra else 0) for r in range(world)]
-        self.v0 = 128 * sum(counts[:rank])
-        self.vn = 128 * counts[rank]
+        from importlib import import_module
+        self.v0, self.vn = import_module("ds41_b200.sharded").shard_plan(VOCAB, world)[rank]
         self.wq, self.ws = make_weights(torch, device, self.vn, 1234 + rank)
         g = torch.Generator(device=device).manual_seed(99)
         self.ring = [torch.randn(batch, HIDDEN, device=device, generator=g).to(torch.bfloat16) for _ in range(16)]
@@ -147,7 +144,6 @@ class HeadSample:
         self.bound = "hbm" if batch <= 128 else "tensor"
         self.sharded = None
         if world > 1:
-            from importlib import import_module
             self.sharded = import_module("ds41_b200.sharded").ShardedSampler(pkg, torch, device, batch, self.v0, self.vn,
                                                                            VOCAB, temperature, top_p)
             self.launches_per_step = 2 + self.sharded.launches_per_step

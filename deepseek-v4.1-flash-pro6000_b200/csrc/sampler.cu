@@ -39,6 +39,7 @@ cudaError_t launch_rows(const RowArgs &a, int rows, cudaStream_t stream) {
 }
 template cudaError_t launch_rows<kModeSample>(const RowArgs &, int, cudaStream_t);
 template cudaError_t launch_rows<kModeStats>(const RowArgs &, int, cudaStream_t);
+template cudaError_t launch_rows<kModeShard>(const RowArgs &, int, cudaStream_t);
 
 }  // namespace ds41
 

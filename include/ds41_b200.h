@@ -36,6 +36,7 @@ extern "C" {
 #define DS41_B200_ROW_TIES (-4)           /* more than 1024 equal logits straddle a top-k / top-p cut */
 #define DS41_B200_ROW_TIMEOUT (-5)        /* a bounded device-side wait expired */
 #define DS41_B200_ROW_DRAFT (-6)          /* draft id out of range or impossible under q (sampling.cpp:44,47) */
+#define DS41_B200_ROW_NOT_COVERED (-8)    /* sharded combine: the candidates of some rank may not contain the whole nucleus; redo the row from full logits */
 #define DS41_B200_ROW_HISTORY (-7)        /* history_len[r] negative or above DS41_B200_MAX_HISTORY */
 
 /* Same layout as ds41_spark_result (spark.h:106-108). */
@@ -135,6 +136,43 @@ int ds41_b200_verify_logits(const ds41_b200_verify_args *args, cudaStream_t stre
  * allocates.  All calls share the array, so calls that could overlap on the GPU must be serialised by the caller. */
 int ds41_b200_verify_logits_static_max_rows(void);
 int ds41_b200_verify_logits_static(const ds41_b200_verify_args *args, cudaStream_t stream);
+
+/* ---- vocabulary-sharded sampling (several GPUs, one rank per GPU) -----------------------------------------------
+ * No counterpart in the reference (single GPU, no collectives: scripts/run.py:228).  Rank r owns the logits of the
+ * contiguous id range [vocab_offset, vocab_offset + vocab_local) (e.g. its slice of the head's weight rows).
+ *   1. every rank: ds41_b200_shard_candidates -> one ds41_b200_shard_row per row (544 bytes);
+ *   2. caller: all-gather of the records into `gathered` [ranks][rows] (ncclAllGather on the same stream);
+ *   3. every rank: ds41_b200_shard_combine -> the same token ids on every rank.
+ * A row whose nucleus may extend beyond some rank's 64 candidates gets status DS41_B200_ROW_NOT_COVERED and
+ * token -1; the caller must then sample that row from its full logits (ds41_b200_sample_logits).  top_p = 1 is
+ * therefore only covered when every shard holds at most 64 allowed ids. */
+#define DS41_B200_SHARD_CANDIDATES 64
+typedef struct ds41_b200_shard_row {
+  double z;
+  float max_logit;
+  int32_t argmax, count, status;
+  int32_t complete; /* 1: cand[] holds every allowed id of the shard */
+  struct { float y; int32_t id; } cand[DS41_B200_SHARD_CANDIDATES];
+} ds41_b200_shard_row;
+typedef struct ds41_b200_shard_args {
+  uint32_t struct_bytes;
+  int32_t rows, vocab_local, vocab_offset;
+  const float *logits;      /* [rows, logits_stride], this rank's id range */
+  int64_t logits_stride;
+  double temperature;
+  ds41_b200_shard_row *out; /* [rows] */
+} ds41_b200_shard_args;
+int ds41_b200_shard_candidates(const ds41_b200_shard_args *args, cudaStream_t stream);
+typedef struct ds41_b200_shard_combine_args {
+  uint32_t struct_bytes;
+  int32_t rows, ranks, vocab;            /* ranks <= 8, vocab = full vocabulary */
+  const ds41_b200_shard_row *gathered;   /* [ranks][rows] */
+  double temperature, top_p;
+  const uint64_t *seeds, *steps;         /* [rows] */
+  uint32_t slot, purpose;
+  int32_t *tokens, *status;              /* [rows] out */
+} ds41_b200_shard_combine_args;
+int ds41_b200_shard_combine(const ds41_b200_shard_combine_args *args, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,135 @@
+"""Host-side logic of the vocabulary-sharded path on CPU: two gloo ranks, the exchange and the escalation of
+uncovered rows run through the real ShardedSampler code; the two CUDA kernels are replaced by a NumPy restatement of
+their algorithm (checked against the oracle's tokens), because no GPU exists in this test."""
+import importlib
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REC = np.dtype([("z", np.float64), ("max", np.float32), ("argmax", np.int32), ("count", np.int32),
+                ("status", np.int32), ("complete", np.int32), ("cand", [("y", np.float32), ("id", np.int32)], 64),
+                ("pad", np.int32)])  # the C struct is 8-byte aligned: 540 -> 544 bytes
+
+
+def test_shard_plan():
+    sys.path.insert(0, ROOT)
+    import __graft_entry__ as entry
+    entry.load_package()
+    plan = importlib.import_module("ds41_b200.sharded").shard_plan
+    assert [n // 128 for _, n in plan(129280, 8)] == [127, 127, 126, 126, 126, 126, 126, 126]
+    assert [n // 128 for _, n in plan(129280, 4)] == [253, 253, 252, 252]
+    assert plan(129280, 2) == [(0, 64640), (64640, 64640)]
+    for v, w in ((129280, 8), (1000, 3), (7, 2), (129281, 5)):
+        p = plan(v, w)
+        assert p[0][0] == 0 and sum(n for _, n in p) == v
+        assert all(p[i][0] + p[i][1] == p[i + 1][0] for i in range(w - 1))
+    assert REC.itemsize == 544
+
+
+def numpy_candidates(x, v0, t):
+    out = np.zeros(x.shape[0], REC)
+    for r, row in enumerate(x):
+        b = int(row.argmax())
+        order = np.lexsort((np.arange(row.size), -row.astype(np.float64)))[:64]
+        out[r]["max"], out[r]["argmax"] = row[b], b + v0
+        out[r]["z"] = np.exp((row.astype(np.float64) - np.float64(row[b])) / t).sum()
+        out[r]["count"], out[r]["complete"] = order.size, int(row.size <= 64)
+        out[r]["cand"]["y"][:order.size] = row[order]
+        out[r]["cand"]["id"][:order.size] = order + v0
+    return out
+
+
+def numpy_combine(records, ranks, t, top, seeds, steps, uniform):
+    rows = records.shape[1]
+    tokens, status = np.full(rows, -1, np.int32), np.zeros(rows, np.int32)
+    for r in range(rows):
+        h = records[:, r]
+        best = max(range(ranks), key=lambda k: (h[k]["max"], -h[k]["argmax"]))
+        m = np.float64(h[best]["max"])
+        z = sum(h[k]["z"] * np.exp((np.float64(h[k]["max"]) - m) / t) for k in range(ranks))
+        y = np.concatenate([h[k]["cand"]["y"][:h[k]["count"]] for k in range(ranks)])
+        ids = np.concatenate([h[k]["cand"]["id"][:h[k]["count"]] for k in range(ranks)])
+        owner = np.concatenate([np.full(h[k]["count"], k) for k in range(ranks)])
+        order = np.lexsort((ids, -y.astype(np.float64)))
+        e = np.exp((y[order].astype(np.float64) - m) / t)
+        mass = np.cumsum(e)
+        pos = int(np.argmax(mass >= top * z)) if (mass >= top * z).any() and top < 1 else -1
+        covered = pos >= 0 and all(h[k]["complete"] or np.where(owner[order] == k)[0].max() > pos for k in range(ranks))
+        if pos < 0 and all(h[k]["complete"] for k in range(ranks)):
+            covered, pos = True, len(order) - 1
+        if not covered:
+            status[r] = -8
+            continue
+        keep = np.sort(order[:pos + 1], kind="stable")
+        keep = keep[np.argsort(ids[keep], kind="stable")]
+        ek = np.exp((y[keep].astype(np.float64) - m) / t)
+        c = np.cumsum(ek)
+        u = uniform(int(seeds[r]), int(steps[r]))
+        hit = np.where(u * c[-1] < c)[0]
+        tokens[r] = ids[keep][hit[0]] if hit.size else ids[keep][-1]
+    return tokens, status
+
+
+def worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import __graft_entry__ as entry
+    import oracle_lib
+    entry.load_package()
+    sh = importlib.import_module("ds41_b200.sharded")
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    orc = oracle_lib.Oracle()
+    rows, vocab = 12, 4096 + 128
+    x = orc.gen_logits(5, rows, vocab, sigma=2.5, zipf_s=1.3)
+    seeds, steps = np.arange(rows, dtype=np.uint64) + 3, np.arange(rows, dtype=np.uint64) * 5
+    failures = []
+    for t, top in ((0.5, 0.9), (1.0, 0.97)):   # the second setting leaves some rows uncovered -> escalation path
+        want, _ = orc.sample_rows(x, t, top, seeds, steps, slot=1, threads=2)
+        v0, vn = sh.shard_plan(vocab, world)[rank]
+
+        class CpuSampler(sh.ShardedSampler):
+            def candidates(self, logits):
+                rec = numpy_candidates(logits.numpy(), self.v0, self.t)
+                self.local.copy_(torch.from_numpy(rec.view(np.uint8).reshape(-1)))
+
+            def combine(self, seeds_t, steps_t, tokens, status, slot=0, purpose=0):
+                rec = self.gathered.numpy().view(REC).reshape(self.world, self.rows)
+                tok, st = numpy_combine(rec, self.world, self.t, self.top_p, seeds_t.numpy().view(np.uint64),
+                                        steps_t.numpy().view(np.uint64), lambda s, p: orc.uniform(s, p, slot, purpose))
+                tokens.copy_(torch.from_numpy(tok)); status.copy_(torch.from_numpy(st))
+
+            def sample_full(self, full, seeds_t, steps_t, slot, purpose):
+                tok, st = orc.sample_rows(full.numpy(), self.t, self.top_p, seeds_t.numpy().view(np.uint64),
+                                          steps_t.numpy().view(np.uint64), slot=slot, purpose=purpose)
+                return torch.from_numpy(tok), torch.from_numpy(st)
+
+        s = CpuSampler(None, torch, torch.device("cpu"), rows, v0, vn, vocab, t, top)
+        tokens, status = torch.empty(rows, dtype=torch.int32), torch.empty(rows, dtype=torch.int32)
+        s.sample(torch.from_numpy(x[:, v0:v0 + vn].copy()), torch.from_numpy(seeds.view(np.int64)),
+                 torch.from_numpy(steps.view(np.int64)), tokens, status, slot=1)
+        if not (tokens.numpy() == want).all():
+            failures.append(f"rank {rank} T={t} top={top}: {tokens.numpy()} != {want}")
+        if (t, top) == (1.0, 0.97) and s.escalated == 0:
+            failures.append("escalation path not exercised")
+        gathered = [torch.empty_like(tokens) for _ in range(world)]
+        dist.all_gather(gathered, tokens)
+        if not all(torch.equal(g, tokens) for g in gathered):
+            failures.append("ranks disagree")
+    out[rank] = failures
+    dist.destroy_process_group()
+
+
+def test_two_rank_exchange_and_escalation_on_gloo():
+    world, port = 2, 29500 + os.getpid() % 2000
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(worker, args=(world, port, out), nprocs=world, join=True)
+        assert len(out) == world
+        for rank in range(world):
+            assert out[rank] == [], out[rank]
