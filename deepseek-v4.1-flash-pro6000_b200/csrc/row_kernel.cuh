@@ -2,6 +2,7 @@
 // the inverse-CDF draw (sampler) or a RowStats record (verifier).  One cluster per row; see row_core.cuh.
 #pragma once
 #include "row_core.cuh"
+#include "row_fast.cuh"
 
 namespace ds41 {
 
@@ -288,6 +289,27 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
     return;
   }
 
+  if constexpr (kMode != kModeShard) {
+    if (status == 0 && t != 0) {
+      const double u = kMode == kModeSample ? philox_uniform(a.seeds[row], a.steps[row], a.slot, a.purpose) : 0.0;
+      const FastOutcome f = fast_small_support(c, max_logit, t, allowed, a.top_k, a.top_p, u, kMode == kModeSample);
+      if (f.applicable) {
+        // ranks other than 0 are done after the gather; rank 0 finishes alone and touches only its own shared memory
+        if (c.rank == 0 && c.tid == 0) {
+          if (kMode == kModeSample) {
+            a.tokens[row] = f.token;
+            if (a.status) a.status[row] = f.status;
+          } else {
+            RowStats st;
+            st.z = f.z; st.e_kept = f.e_kept; st.max_logit = max_logit; st.argmax = best_id; st.cut = f.cut;
+            st.kept = f.kept; st.entered = f.entered; st.status = f.status; st.pad = 0;
+            a.stats[row] = st;
+          }
+        }
+        return;
+      }
+    }
+  }
   if (status == 0 && t == 0) {
     token = best_id;
     kept = 1; z = 1; e_kept = 1;
