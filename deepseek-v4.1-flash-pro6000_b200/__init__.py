@@ -44,7 +44,7 @@ class SampleArgs(C.Structure):
                 ("temperature", _f64), ("top_p", _f64), ("top_k", _i32), ("repetition", _f32), ("presence", _f32),
                 ("frequency", _f32), ("history", _P), ("history_stride", _i64), ("history_len", _P), ("mask", _P),
                 ("mask_stride", _i64), ("seeds", _P), ("steps", _P), ("slot", _u32), ("purpose", _u32),
-                ("tokens", _P), ("status", _P)]
+                ("tokens", _P), ("status", _P), ("scratch", _P), ("scratch_bytes", C.c_size_t)]
 
 
 class VerifyArgs(C.Structure):
@@ -70,6 +70,10 @@ def lib():
         L.ds41_spark_uniform_v2.restype = _f64
         L.ds41_spark_uniform_v2.argtypes = [_u64, _u64, _u32, _u32, _u64]
         L.ds41_b200_sample_logits.argtypes = [C.POINTER(SampleArgs), _P]
+        L.ds41_b200_sample_scratch_bytes.restype = C.c_size_t
+        L.ds41_b200_sample_scratch_bytes.argtypes = [C.c_int, C.c_int]
+        L.ds41_b200_verify_scratch_bytes_for.restype = C.c_size_t
+        L.ds41_b200_verify_scratch_bytes_for.argtypes = [C.c_int, C.c_int, C.c_int]
         L.ds41_b200_verify_logits.argtypes = [C.POINTER(VerifyArgs), _P]
         L.ds41_b200_verify_logits_static.argtypes = [C.POINTER(VerifyArgs), _P]
         L.ds41_b200_verify_logits_static_max_rows.restype = C.c_int
@@ -139,11 +143,17 @@ class AttemptCounter:
         return out
 
 
+def sample_scratch_bytes(rows, vocab):
+    return lib().ds41_b200_sample_scratch_bytes(rows, vocab)
+
+
 def sample_logits(logits, temperature, top_p, seeds, steps, slot=0, purpose=Purpose.Target, top_k=0, history=None,
-                  history_len=None, repetition=1.0, presence=0.0, frequency=0.0, mask=None, tokens=None, status=None):
+                  history_len=None, repetition=1.0, presence=0.0, frequency=0.0, mask=None, tokens=None, status=None,
+                  scratch="auto"):
     """Batched probabilities() + sample() / argmax() on device logits [rows, vocab] (fp32).
 
     seeds/steps: int64 CUDA tensors holding the uint64 Philox key and attempt counter of each row.
+    scratch: "auto" (allocate what the streaming path needs), None (cluster kernel only) or a uint8 CUDA tensor.
     Returns (tokens int32 [rows], status int32 [rows]); see ds41_b200.h for the status words."""
     logits = _dev(logits, torch.float32, "logits") if logits.is_contiguous() else logits
     if logits.dim() != 2 or logits.stride(1) != 1 or not logits.is_cuda or logits.dtype != torch.float32:
@@ -172,13 +182,18 @@ def sample_logits(logits, temperature, top_p, seeds, steps, slot=0, purpose=Purp
     a.seeds, a.steps = seeds.data_ptr(), steps.data_ptr()
     a.slot, a.purpose = slot, int(purpose)
     a.tokens, a.status = tokens.data_ptr(), status.data_ptr()
+    if isinstance(scratch, str):
+        usable = history is None and mask is None and top_k <= 64
+        scratch = torch.empty(sample_scratch_bytes(rows, vocab), dtype=torch.uint8, device=logits.device) if usable else None
+    a.scratch = scratch.data_ptr() if scratch is not None else None
+    a.scratch_bytes = scratch.numel() if scratch is not None else 0
     with torch.cuda.device(logits.device):
         _check(lib().ds41_b200_sample_logits(C.byref(a), _stream()), "ds41_b200_sample_logits")
     return tokens, status
 
 
-def verify_scratch_bytes(sequences, drafts):
-    return lib().ds41_b200_verify_scratch_bytes(sequences, drafts)
+def verify_scratch_bytes(sequences, drafts, vocab=MAX_VOCAB):
+    return lib().ds41_b200_verify_scratch_bytes_for(sequences, drafts, vocab)
 
 
 def verify_logits(target_logits, draft_logits, draft_ids, drafts, temperature, top_p, seeds, steps, scratch=None,
@@ -198,7 +213,7 @@ def verify_logits(target_logits, draft_logits, draft_ids, drafts, temperature, t
         raise ValueError("speculative row count")
     sequences = rows // (drafts + 1)
     device = target_logits.device
-    need = verify_scratch_bytes(sequences, drafts)
+    need = verify_scratch_bytes(sequences, drafts, vocab)
     if scratch is None:
         scratch = torch.empty(need, dtype=torch.uint8, device=device)
     if results is None:

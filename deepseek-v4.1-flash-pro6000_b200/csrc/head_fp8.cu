@@ -11,8 +11,9 @@
 // tcgen05.mma (one TMEM lane per vocabulary row) and the batch is its N dimension (16..128 TMEM columns), so a batch
 // of 1 wastes no tensor-core rows and the fp32 accumulators of one vocabulary row live in one thread of the
 // epilogue.  Per CTA: warp 0 streams W and A tiles with TMA (128-byte swizzle) into a ring of shared-memory stages,
-// warp 1 issues four K=32 tcgen05.mma per 128-wide K block into one of two TMEM accumulators, warps 2-5 pull each
-// finished K block out of TMEM (tcgen05.ld), apply the two scales in fp32 and keep the running sums in registers.
+// warp 1 issues four K=32 tcgen05.mma per 128-wide K block into one of four TMEM accumulators, the epilogue warps
+// (one or two groups of four) pull each finished K block out of TMEM (tcgen05.ld), apply the combined scale in fp32
+// and keep the running sums in registers.
 // Every wait is bounded; on expiry the kernel raises *error_flag, frees its TMEM and returns.
 #include "ds41_b200.h"
 #include "host_error.h"
@@ -27,7 +28,7 @@ namespace {
 
 constexpr int kTileN = 128;   // vocabulary rows per tile (UMMA M)
 constexpr int kTileK = 128;   // K elements per block = one 128-byte swizzle row of e4m3
-constexpr int kThreadsHead = 192;
+constexpr int kAccBufs = 4;   // TMEM accumulators in flight (K blocks between the MMA issuer and the epilogue)
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -131,20 +132,22 @@ struct HeadArgs {
   int *error_flag;       // device word, raised on a wait timeout (may be null)
 };
 
-template <int kCols>
-__global__ void __launch_bounds__(kThreadsHead, 1)
+// kGroups epilogue warpgroups of 4 warps split the batch columns between them.
+template <int kCols, int kGroups>
+__global__ void __launch_bounds__(64 + 128 * kGroups, 1)
 head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, HeadArgs p) {
   constexpr int kStages = HeadSmem<kCols>::kStages;
   constexpr int kStageBytes = HeadSmem<kCols>::kStageBytes;
-  constexpr uint32_t kTmemCols = 2 * kCols < 32 ? 32 : 2 * kCols;
+  constexpr uint32_t kTmemCols = kAccBufs * kCols < 32 ? 32 : kAccBufs * kCols;
+  constexpr int kEpiThreads = 128 * kGroups, kMyCols = kCols / kGroups;
   extern __shared__ __align__(1024) unsigned char smem[];
   // carve: [stages][W tile 16 KB | A tile kCols*128 B], then the activation-scale table, then barriers
   unsigned char *tiles = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~uintptr_t(1023));
   float *sx = reinterpret_cast<float *>(tiles + size_t(kStages) * kStageBytes);  // [K/128][kCols]
   const int kblocks = p.K / kTileK;
   uint64_t *bars = reinterpret_cast<uint64_t *>(sx + size_t(kblocks) * kCols);
-  uint64_t *full = bars, *empty = bars + kStages, *acc_full = bars + 2 * kStages, *acc_empty = bars + 2 * kStages + 2;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 4);
+  uint64_t *full = bars, *empty = bars + kStages, *acc_full = bars + 2 * kStages, *acc_empty = acc_full + kAccBufs;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + kAccBufs);
   int *abort_word = reinterpret_cast<int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -155,7 +158,7 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   if (threadIdx.x == 0) {
     *abort_word = 0;
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < kAccBufs; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4 * kGroups); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {  // TMEM allocation by one full warp; the address lands in shared memory
@@ -201,64 +204,77 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           umma_commit(&empty[stage]);    // stage may be refilled once these MMAs have read it
           umma_commit(&acc_full[acc]);   // accumulator of this K block is complete
           if (++stage == kStages) { stage = 0; phase ^= 1; }
-          if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+          if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1; }
         }
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue: 4 warps, one TMEM lane quadrant each
+    // ------------------------------------------------------------------ epilogue: 4 warps per group, one TMEM lane
+    // quadrant each; group g owns the batch columns [g*kMyCols, (g+1)*kMyCols)
     const int quad = warp & 3;                      // TMEM lanes [32*quad, 32*quad+32) are readable by this warp
-    const int et = threadIdx.x - 64;                // 0..127
+    const int et = threadIdx.x - 64;                // 0..kEpiThreads-1
+    const int group = et >> 7, col0 = group * kMyCols;
     uint32_t acc = 0, acc_phase = 0;
     bool alive = true;  // warp-uniform; once false the remaining tiles are walked without waiting or computing,
-                        // so that all 128 epilogue threads still meet at every named barrier
+                        // so that all epilogue threads still meet at every named barrier
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       const int nt = tile / b_tiles, bt = tile % b_tiles;
-      // activation scales of this batch tile, transposed to [kb][column]
-      asm volatile("bar.sync 1, 128;" ::: "memory");  // previous tile's readers are done with sx
-      for (int i = et; i < kblocks * kCols; i += 128) {
-        const int kb = i / kCols, col = i % kCols, m = bt * kCols + col;
-        sx[i] = m < p.M ? __ldg(p.a_scale + size_t(m) * kblocks + kb) : 0.f;
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      float sum[kCols];
-#pragma unroll
-      for (int c = 0; c < kCols; ++c) sum[c] = 0.f;
+      // combined scales of this tile, sx[kb][column] = a_scale[m, kb] * w_scale[nt, kb]
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");  // previous tile's readers are done with sx
       const float *wsc = p.w_scale + size_t(nt) * kblocks;
+      for (int i = et; i < kblocks * kCols; i += kEpiThreads) {
+        const int kb = i / kCols, col = i % kCols, m = bt * kCols + col;
+        sx[i] = m < p.M ? __ldg(p.a_scale + size_t(m) * kblocks + kb) * __ldg(wsc + kb) : 0.f;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+      float sum[kMyCols];
+#pragma unroll
+      for (int c = 0; c < kMyCols; ++c) sum[c] = 0.f;
       for (int kb = 0; kb < kblocks && alive; ++kb) {
         alive = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], acc_phase, ab));
         if (!alive) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const float sw = __ldg(wsc + kb);
-        const uint32_t taddr = tmem_base + acc * kCols + (uint32_t(quad * 32) << 16);
-        const float *sxk = sx + kb * kCols;
-        if constexpr (kCols == 16) {
+        const uint32_t taddr = tmem_base + acc * kCols + col0 + (uint32_t(quad * 32) << 16);
+        const float4 *sxk = reinterpret_cast<const float4 *>(sx + kb * kCols + col0);
+        if constexpr (kMyCols == 16) {
           uint32_t r[32];
           tmem_ld16(taddr, r);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int c = 0; c < 16; ++c) sum[c] = fmaf(__uint_as_float(r[c]), sw * sxk[c], sum[c]);
+          for (int c = 0; c < 16; c += 4) {
+            const float4 sc = sxk[c >> 2];
+            sum[c] = fmaf(__uint_as_float(r[c]), sc.x, sum[c]);
+            sum[c + 1] = fmaf(__uint_as_float(r[c + 1]), sc.y, sum[c + 1]);
+            sum[c + 2] = fmaf(__uint_as_float(r[c + 2]), sc.z, sum[c + 2]);
+            sum[c + 3] = fmaf(__uint_as_float(r[c + 3]), sc.w, sum[c + 3]);
+          }
         } else {
 #pragma unroll
-          for (int c0 = 0; c0 < kCols; c0 += 32) {
+          for (int c0 = 0; c0 < kMyCols; c0 += 32) {
             uint32_t r[32];
             tmem_ld32(taddr + c0, r);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int c = 0; c < 32; ++c) sum[c0 + c] = fmaf(__uint_as_float(r[c]), sw * sxk[c0 + c], sum[c0 + c]);
+            for (int c = 0; c < 32; c += 4) {
+              const float4 sc = sxk[(c0 + c) >> 2];
+              sum[c0 + c] = fmaf(__uint_as_float(r[c]), sc.x, sum[c0 + c]);
+              sum[c0 + c + 1] = fmaf(__uint_as_float(r[c + 1]), sc.y, sum[c0 + c + 1]);
+              sum[c0 + c + 2] = fmaf(__uint_as_float(r[c + 2]), sc.z, sum[c0 + c + 2]);
+              sum[c0 + c + 3] = fmaf(__uint_as_float(r[c + 3]), sc.w, sum[c0 + c + 3]);
+            }
           }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[acc]);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1; }
       }
       if (alive) {
         const int n = nt * kTileN + quad * 32 + lane;
         if (n < p.N) {
 #pragma unroll
-          for (int c = 0; c < kCols; ++c) {
-            const int m = bt * kCols + c;
+          for (int c = 0; c < kMyCols; ++c) {
+            const int m = bt * kCols + col0 + c;
             if (m < p.M) p.logits[size_t(m) * p.ldl + n] = sum[c];
           }
         }
@@ -326,23 +342,23 @@ bool make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, 
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int kCols>
+template <int kCols, int kGroups>
 cudaError_t launch_head(const CUtensorMap &mw, const CUtensorMap &ma, const HeadArgs &p, int sms, cudaStream_t stream) {
   constexpr int kStages = HeadSmem<kCols>::kStages;
   const size_t smem = 1024 + size_t(kStages) * HeadSmem<kCols>::kStageBytes + size_t(p.K / kTileK) * kCols * 4 +
-                      (2 * kStages + 4) * 8 + 16;
+                      (2 * kStages + 2 * kAccBufs) * 8 + 16;
   static thread_local int configured = -1;
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (configured != dev) {
-    e = cudaFuncSetAttribute(head_fp8_kernel<kCols>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    e = cudaFuncSetAttribute(head_fp8_kernel<kCols, kGroups>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     configured = dev;
   }
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
   const int tiles = ((p.N + kTileN - 1) / kTileN) * ((p.M + kCols - 1) / kCols);
-  head_fp8_kernel<kCols><<<tiles < sms ? tiles : sms, kThreadsHead, smem, stream>>>(mw, ma, p);
+  head_fp8_kernel<kCols, kGroups><<<tiles < sms ? tiles : sms, 64 + 128 * kGroups, smem, stream>>>(mw, ma, p);
   return cudaGetLastError();
 }
 
@@ -378,10 +394,10 @@ extern "C" int ds41_b200_head_fp8(const void *a_e4m3, const float *a_scale, cons
     return invalid("cuTensorMapEncodeTiled failed");
   HeadArgs p{a_scale, w_scale, logits, logits_stride, M, N, K, error_flag};
   switch (cols) {
-    case 16: e = launch_head<16>(mw, ma, p, sms, stream); break;
-    case 32: e = launch_head<32>(mw, ma, p, sms, stream); break;
-    case 64: e = launch_head<64>(mw, ma, p, sms, stream); break;
-    default: e = launch_head<128>(mw, ma, p, sms, stream); break;
+    case 16: e = launch_head<16, 1>(mw, ma, p, sms, stream); break;
+    case 32: e = launch_head<32, 1>(mw, ma, p, sms, stream); break;
+    case 64: e = launch_head<64, 1>(mw, ma, p, sms, stream); break;
+    default: e = launch_head<128, 2>(mw, ma, p, sms, stream); break;
   }
   return int(e);
 }

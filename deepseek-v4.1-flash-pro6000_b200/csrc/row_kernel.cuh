@@ -6,19 +6,7 @@
 
 namespace ds41 {
 
-enum RowMode { kModeSample = 0, kModeStats = 1, kModeShard = 2 };
-
-// Per-row record a vocabulary shard publishes for the cross-rank combine (layout = ds41_b200_shard_row).
-constexpr int kShardCand = 64;
-struct ShardRow {
-  double z;         // sum over the shard's allowed ids of exp((y - max_logit)/T), relative to the SHARD's maximum
-  float max_logit;  // shard maximum
-  int argmax;       // its global id (first maximum)
-  int count;        // candidates present (all allowed ids of the shard if there are at most kShardCand)
-  int status;       // 0 or a negative row error
-  int complete;     // 1: the candidates are ALL allowed ids of the shard
-  struct { float y; int id; } cand[kShardCand];  // the shard's first ids in the order (y desc, id asc), unordered
-};
+enum RowMode { kModeSample = 0, kModeStats = 1 };
 
 struct RowArgs {
   const float *logits;
@@ -38,8 +26,7 @@ struct RowArgs {
   int32_t *tokens;
   int32_t *status;
   RowStats *stats;
-  ShardRow *shard_out;  // kModeShard
-  int id_offset;        // global id of the shard's first logit
+  int only_uncovered;  // 1: process only rows the streaming path reported as not covered, leave the others alone
 };
 
 // Region sums of a non-negative per-id value (value(j) for local index j < len, 0 for ids outside the support):
@@ -146,6 +133,10 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
   RowSmem *s = reinterpret_cast<RowSmem *>(smem_raw);
   RowCtx c = make_ctx(s, a.vocab);
   const int row = blockIdx.x / c.nranks;
+  if (a.only_uncovered) {  // same answer in every CTA of the cluster, so the whole cluster leaves together
+    const int st = kMode == kModeSample ? a.status[row] : a.stats[row].status;
+    if (st != -8) return;
+  }
   const float *logits = a.logits + size_t(row) * a.logits_stride;
 
   bool used_tma;
@@ -240,56 +231,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
   double z = 0, e_kept = 0;
   int token = -1;
 
-  if constexpr (kMode == kModeShard) {
-    // ---- vocabulary shard: publish maximum, partial normaliser and the first kShardCand ids of the stable order
-    if (status == 0 && t != 0) {
-      if (allowed > kShardCand) {
-        CutResult r = find_cut<false>(c, max_logit, 16.f / kBins, kShardCand, 0.0, allowed,
-                                      [](float y, int) { return y > -CUDART_INF_F; }, weight);
-        if (r.error) status = r.error;
-        else cut = r.cut;
-      }
-      if (status == 0) {
-        region_sums(c, [s, weight](int j) { const float y = s->y[j]; return y > -CUDART_INF_F ? weight(y) : 0.0; });
-        double block_total = 0;
-        for (int w = 0; w < kWarps; ++w) block_total += s->warp_sum[w];
-        Slot mine{};
-        mine.d[0] = block_total;
-        if (c.tid == 0) s->list_count = 0;
-        const Slot *all = exchange(c, mine);  // its barrier also publishes the list_count reset
-        for (int r = 0; r < c.nranks; ++r) z += all[r].d[0];
-        int *list_count0 = c.cluster.map_shared_rank(&s->list_count, 0);
-        float *list_y0 = c.cluster.map_shared_rank(s->u.w.list_y, 0);
-        int *list_id0 = c.cluster.map_shared_rank(s->u.w.list_id, 0);
-        for (int it = 0; it < c.region; it += 32) {
-          const int j = c.warp * c.region + it + c.lane;
-          if (j >= c.len) continue;
-          const float y = s->y[j];
-          if (y > -CUDART_INF_F && survives(y, c.begin + j, cut)) {
-            const int slot = atomicAdd(list_count0, 1);
-            if (slot < kShardCand) { list_y0[slot] = y; list_id0[slot] = c.begin + j + a.id_offset; }
-          }
-        }
-        c.cluster.sync();
-      }
-    }
-    if (c.rank == 0) {
-      ShardRow *out = a.shard_out + row;
-      const int n = (status == 0 && t != 0) ? min(s->list_count, kShardCand) : 0;
-      if (c.tid < kShardCand) {
-        out->cand[c.tid].y = c.tid < n ? s->u.w.list_y[c.tid] : -CUDART_INF_F;
-        out->cand[c.tid].id = c.tid < n ? s->u.w.list_id[c.tid] : -1;
-      }
-      if (c.tid == 0) {
-        out->z = z; out->max_logit = max_logit; out->argmax = status == 0 ? best_id + a.id_offset : -1;
-        out->count = n; out->status = status; out->complete = allowed <= kShardCand ? 1 : 0;
-      }
-    }
-    c.cluster.sync();
-    return;
-  }
-
-  if constexpr (kMode != kModeShard) {
+  {
     if (status == 0 && t != 0) {
       const double u = kMode == kModeSample ? philox_uniform(a.seeds[row], a.steps[row], a.slot, a.purpose) : 0.0;
       const FastOutcome f = fast_small_support(c, max_logit, t, allowed, a.top_k, a.top_p, u, kMode == kModeSample);

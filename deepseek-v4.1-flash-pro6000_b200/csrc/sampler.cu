@@ -1,6 +1,7 @@
 // C-ABI entry points of the sampler and of the host-side Philox helpers.  See include/ds41_b200.h.
 #include "ds41_b200.h"
 #include "row_kernel.cuh"
+#include "stream_types.cuh"
 #include "host_error.h"
 #include <cmath>
 
@@ -39,11 +40,19 @@ cudaError_t launch_rows(const RowArgs &a, int rows, cudaStream_t stream) {
 }
 template cudaError_t launch_rows<kModeSample>(const RowArgs &, int, cudaStream_t);
 template cudaError_t launch_rows<kModeStats>(const RowArgs &, int, cudaStream_t);
-template cudaError_t launch_rows<kModeShard>(const RowArgs &, int, cudaStream_t);
+
+int chunks_for(int vocab);
+cudaError_t launch_chunks(const ChunkArgs &a, int rows, cudaStream_t stream);
+cudaError_t launch_combine(const CombineArgs &a, bool stats, cudaStream_t stream);
 
 }  // namespace ds41
 
 using namespace ds41;
+
+extern "C" size_t ds41_b200_sample_scratch_bytes(int rows, int vocab) {
+  if (rows < 1 || vocab < 1 || vocab > DS41_B200_MAX_VOCAB) return 0;
+  return size_t(rows) * chunks_for(vocab) * sizeof(ChunkRecord) + ((size_t(rows) * 4 + 15) & ~size_t(15));
+}
 
 extern "C" uint32_t ds41_spark_rng_word_v2(uint64_t seed, uint64_t step, uint32_t slot, uint32_t purpose, uint64_t draw) {
   if (slot > 5 || purpose > 3 || draw / 4 > UINT32_MAX) { set_error("Philox v2 address out of range"); return 0; }
@@ -76,5 +85,24 @@ extern "C" int ds41_b200_sample_logits(const ds41_b200_sample_args *p, cudaStrea
   a.mask = p->mask; a.mask_stride = p->mask_stride;
   a.seeds = p->seeds; a.steps = p->steps; a.slot = p->slot; a.purpose = p->purpose;
   a.tokens = p->tokens; a.status = p->status; a.stats = nullptr;
+  const bool penalised = p->history && (p->repetition != 1.f || p->presence != 0.f || p->frequency != 0.f);
+  const size_t need = ds41_b200_sample_scratch_bytes(p->rows, p->vocab);
+  const bool streaming = p->scratch && p->scratch_bytes >= need && !(reinterpret_cast<uintptr_t>(p->scratch) & 15u) &&
+                         !penalised && !p->mask && p->top_k <= kCand &&
+                         (p->top_p < 1.0 || p->top_k > 0 || p->temperature == 0);  // a full-vocabulary draw is never covered
+  if (!streaming) return int(launch_rows<kModeSample>(a, p->rows, stream));
+  // streaming path: chunk records -> combine -> cluster kernel only for the rows the combine could not cover
+  const int chunks = chunks_for(p->vocab);
+  ChunkRecord *records = static_cast<ChunkRecord *>(p->scratch);
+  int32_t *status = p->status ? p->status : reinterpret_cast<int32_t *>(records + size_t(p->rows) * chunks);
+  ChunkArgs c{p->logits, p->logits_stride, p->vocab, 0, chunks, a.temperature, records};
+  cudaError_t e = launch_chunks(c, p->rows, stream);
+  if (e != cudaSuccess) return int(e);
+  CombineArgs m{records, p->rows, 1, chunks, p->vocab, a.temperature, p->top_p, p->top_k, p->seeds, p->steps, p->slot,
+                p->purpose, p->tokens, status, nullptr};
+  e = launch_combine(m, false, stream);
+  if (e != cudaSuccess) return int(e);
+  a.status = status;
+  a.only_uncovered = 1;
   return int(launch_rows<kModeSample>(a, p->rows, stream));
 }

@@ -12,6 +12,7 @@
 #include "ds41_b200.h"
 #include "host_error.h"
 #include "row_kernel.cuh"
+#include "stream_types.cuh"
 #include <cmath>
 
 namespace ds41 {
@@ -19,6 +20,9 @@ namespace ds41 {
 template <int kMode>
 cudaError_t launch_rows(const RowArgs &a, int rows, cudaStream_t stream);
 int cluster_size_for(int vocab);
+int chunks_for(int vocab);
+cudaError_t launch_chunks(const ChunkArgs &a, int rows, cudaStream_t stream);
+cudaError_t launch_combine(const CombineArgs &a, bool stats, cudaStream_t stream);
 
 struct VerifyArgs {
   const float *target, *draft;
@@ -125,9 +129,13 @@ __global__ void __launch_bounds__(kThreads, 2) verify_kernel(VerifyArgs a) {
 
 using namespace ds41;
 
+extern "C" size_t ds41_b200_verify_scratch_bytes_for(int sequences, int drafts, int vocab) {
+  if (sequences < 1 || drafts < 0 || drafts > 5 || vocab < 1 || vocab > DS41_B200_MAX_VOCAB) return 0;
+  const size_t rows = size_t(sequences) * size_t(2 * drafts + 1);
+  return rows * sizeof(RowStats) + rows * chunks_for(vocab) * sizeof(ChunkRecord);
+}
 extern "C" size_t ds41_b200_verify_scratch_bytes(int sequences, int drafts) {
-  if (sequences < 1 || drafts < 0 || drafts > 5) return 0;
-  return size_t(sequences) * size_t(2 * drafts + 1) * sizeof(RowStats);
+  return ds41_b200_verify_scratch_bytes_for(sequences, drafts, DS41_B200_MAX_VOCAB);
 }
 
 extern "C" int ds41_b200_verify_logits(const ds41_b200_verify_args *p, cudaStream_t stream) {
@@ -140,21 +148,39 @@ extern "C" int ds41_b200_verify_logits(const ds41_b200_verify_args *p, cudaStrea
   if (!p->target_logits || !p->seeds || !p->steps || !p->results ||
       (p->drafts && (!p->draft_ids || (!p->draft_logits && !greedy))))
     return invalid("verify arguments");
-  if (!p->scratch || p->scratch_bytes < ds41_b200_verify_scratch_bytes(p->sequences, p->drafts) ||
-      (reinterpret_cast<uintptr_t>(p->scratch) & 15u))
+  const size_t stat_rows = size_t(p->sequences) * size_t(2 * p->drafts + 1);
+  if (!p->scratch || p->scratch_bytes < stat_rows * sizeof(RowStats) || (reinterpret_cast<uintptr_t>(p->scratch) & 15u))
     return invalid("verify scratch too small or misaligned");
   RowStats *pstats = static_cast<RowStats *>(p->scratch);
   RowStats *qstats = pstats + size_t(p->sequences) * (p->drafts + 1);
+  // with room for the chunk records the row statistics come from the streaming path (cluster kernel only for rows
+  // it cannot cover); with statistics-only scratch every row goes through the cluster kernel
+  const bool streaming = p->scratch_bytes >= ds41_b200_verify_scratch_bytes_for(p->sequences, p->drafts, p->vocab);
+  ChunkRecord *records = reinterpret_cast<ChunkRecord *>(pstats + stat_rows);
   RowArgs a{};
   a.vocab = p->vocab; a.logits_stride = p->vocab;
   a.temperature = p->temperature > 0 ? std::fmax(p->temperature, 1e-5) : 0.0;
   a.top_p = p->top_p; a.top_k = 0; a.repetition = 1.f;
-  a.logits = p->target_logits; a.stats = pstats;
-  cudaError_t e = launch_rows<kModeStats>(a, p->sequences * (p->drafts + 1), stream);
+  cudaError_t e = cudaSuccess;
+  auto row_stats = [&](const float *logits, RowStats *stats, int rows, ChunkRecord *rec) -> cudaError_t {
+    a.logits = logits; a.stats = stats; a.only_uncovered = 0;
+    if (streaming) {
+      const int chunks = chunks_for(p->vocab);
+      ChunkArgs c{logits, p->vocab, p->vocab, 0, chunks, a.temperature, rec};
+      cudaError_t err = launch_chunks(c, rows, stream);
+      if (err != cudaSuccess) return err;
+      CombineArgs m{rec, rows, 1, chunks, p->vocab, a.temperature, p->top_p, 0, nullptr, nullptr, 0, 0, nullptr, nullptr, stats};
+      err = launch_combine(m, true, stream);
+      if (err != cudaSuccess) return err;
+      a.only_uncovered = 1;
+    }
+    return launch_rows<kModeStats>(a, rows, stream);
+  };
+  e = row_stats(p->target_logits, pstats, p->sequences * (p->drafts + 1), records);
   if (e != cudaSuccess) return int(e);
   if (p->drafts && !greedy) {
-    a.logits = p->draft_logits; a.stats = qstats;
-    e = launch_rows<kModeStats>(a, p->sequences * p->drafts, stream);
+    e = row_stats(p->draft_logits, qstats, p->sequences * p->drafts,
+                  records + size_t(p->sequences) * (p->drafts + 1) * chunks_for(p->vocab));
     if (e != cudaSuccess) return int(e);
   }
   static thread_local int configured_device = -1;

@@ -1,7 +1,7 @@
 """Vocabulary-sharded sampling across the GPUs of one node (one process per GPU, torch.distributed for the exchange).
 
 Rank r owns the contiguous id range produced by `shard_plan` (128-row blocks of the head's weight matrix, uneven by
-at most one block).  Per step: local candidates (CUDA) -> one all-gather of 544-byte records per row (NCCL on GPUs,
+at most one block).  Per step: local candidates (CUDA) -> one all-gather of 544-byte records (one per 8192 ids) per row (NCCL on GPUs,
 gloo in the CPU tests) -> combine (CUDA, replicated on every rank).  Rows the combine cannot certify as covered are
 re-sampled from their full logits, gathered only for those rows.
 """
@@ -27,30 +27,40 @@ def shard_plan(vocab, world, block=128):
     return plan
 
 
+CHUNK_IDS = 8192
+
+
+def chunks_for(vocab_local):
+    return (vocab_local + CHUNK_IDS - 1) // CHUNK_IDS
+
+
 class ShardArgs(C.Structure):
     _fields_ = [("struct_bytes", C.c_uint32), ("rows", C.c_int32), ("vocab_local", C.c_int32),
-                ("vocab_offset", C.c_int32), ("logits", C.c_void_p), ("logits_stride", C.c_int64),
-                ("temperature", C.c_double), ("out", C.c_void_p)]
+                ("vocab_offset", C.c_int32), ("chunks", C.c_int32), ("logits", C.c_void_p),
+                ("logits_stride", C.c_int64), ("temperature", C.c_double), ("out", C.c_void_p)]
 
 
 class CombineArgs(C.Structure):
-    _fields_ = [("struct_bytes", C.c_uint32), ("rows", C.c_int32), ("ranks", C.c_int32), ("vocab", C.c_int32),
-                ("gathered", C.c_void_p), ("temperature", C.c_double), ("top_p", C.c_double), ("seeds", C.c_void_p),
-                ("steps", C.c_void_p), ("slot", C.c_uint32), ("purpose", C.c_uint32), ("tokens", C.c_void_p),
-                ("status", C.c_void_p)]
+    _fields_ = [("struct_bytes", C.c_uint32), ("rows", C.c_int32), ("ranks", C.c_int32), ("chunks", C.c_int32),
+                ("vocab", C.c_int32), ("gathered", C.c_void_p), ("temperature", C.c_double), ("top_p", C.c_double),
+                ("top_k", C.c_int32), ("seeds", C.c_void_p), ("steps", C.c_void_p), ("slot", C.c_uint32),
+                ("purpose", C.c_uint32), ("tokens", C.c_void_p), ("status", C.c_void_p)]
 
 
 class ShardedSampler:
     launches_per_step = 2
 
-    def __init__(self, pkg, torch_mod, device, rows, vocab_offset, vocab_local, vocab, temperature, top_p, group=None):
+    def __init__(self, pkg, torch_mod, device, rows, vocab_offset, vocab_local, vocab, temperature, top_p, group=None,
+                 world=None):
         self.pkg, self.device, self.rows = pkg, device, rows
         self.v0, self.vn, self.vocab = vocab_offset, vocab_local, vocab
         self.t, self.top_p, self.group = temperature, top_p, group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.world = world or (dist.get_world_size(group) if dist.is_initialized() else 1)
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self.local = torch.empty(rows * SHARD_ROW_BYTES, dtype=torch.uint8, device=device)
-        self.gathered = torch.empty(self.world * rows * SHARD_ROW_BYTES, dtype=torch.uint8, device=device)
+        # every rank publishes the same number of 8192-id chunk records per row (short shards pad with empty ones)
+        self.chunks = max(chunks_for(n) for _, n in shard_plan(vocab, self.world))
+        self.local = torch.empty(rows * self.chunks * SHARD_ROW_BYTES, dtype=torch.uint8, device=device)
+        self.gathered = torch.empty(self.world * rows * self.chunks * SHARD_ROW_BYTES, dtype=torch.uint8, device=device)
         self._lib = None
         self.escalated = 0
 
@@ -66,16 +76,16 @@ class ShardedSampler:
         return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
     def candidates(self, logits):
-        a = ShardArgs(C.sizeof(ShardArgs), self.rows, self.vn, self.v0, logits.data_ptr(), logits.stride(0), self.t,
-                      self.local.data_ptr())
+        a = ShardArgs(C.sizeof(ShardArgs), self.rows, self.vn, self.v0, self.chunks, logits.data_ptr(),
+                      logits.stride(0), self.t, self.local.data_ptr())
         rc = self.lib.ds41_b200_shard_candidates(C.byref(a), self._stream())
         if rc:
             raise RuntimeError(f"ds41_b200_shard_candidates: cudaError {rc} ({self.pkg.last_error()})")
 
     def combine(self, seeds, steps, tokens, status, slot=0, purpose=0):
-        a = CombineArgs(C.sizeof(CombineArgs), self.rows, self.world, self.vocab, self.gathered.data_ptr(), self.t,
-                        self.top_p, seeds.data_ptr(), steps.data_ptr(), slot, purpose, tokens.data_ptr(),
-                        status.data_ptr())
+        a = CombineArgs(C.sizeof(CombineArgs), self.rows, self.world, self.chunks, self.vocab,
+                        self.gathered.data_ptr(), self.t, self.top_p, 0, seeds.data_ptr(), steps.data_ptr(), slot,
+                        purpose, tokens.data_ptr(), status.data_ptr())
         rc = self.lib.ds41_b200_shard_combine(C.byref(a), self._stream())
         if rc:
             raise RuntimeError(f"ds41_b200_shard_combine: cudaError {rc} ({self.pkg.last_error()})")

@@ -100,7 +100,13 @@ typedef struct ds41_b200_sample_args {
   uint32_t slot, purpose;     /* slot 0..5, purpose 0..3 (spark.h:96) */
   int32_t *tokens;            /* [rows] out */
   int32_t *status;            /* [rows] out, see above; may be NULL */
+  void *scratch;              /* optional device scratch of ds41_b200_sample_scratch_bytes(rows, vocab) bytes, 16-byte
+                                 aligned.  With it, rows without penalties / bitmask and with top_k <= 64 take the
+                                 streaming path (one pass of independent CTAs + a per-row combine); rows that path
+                                 cannot cover, and calls without scratch, use the cluster kernel.  Same results. */
+  size_t scratch_bytes;
 } ds41_b200_sample_args;
+size_t ds41_b200_sample_scratch_bytes(int rows, int vocab);
 int ds41_b200_sample_logits(const ds41_b200_sample_args *args, cudaStream_t stream);
 
 /* ---- MTP speculative verification from logits ---------------------------------------------------------------
@@ -110,7 +116,8 @@ int ds41_b200_sample_logits(const ds41_b200_sample_args *args, cudaStream_t stre
  * the draft logits, both through the same temperature/top-p rule, so q is the measure the proposal was drawn
  * from (spark.h:101-105).  Sequence s uses the address (seeds[s], steps[s], slot = position, purpose =
  * ACCEPT / RESIDUAL / TARGET) exactly as the reference.  temperature 0 selects the greedy rule (draft_logits
- * may then be NULL).  `scratch` is caller-owned device memory of ds41_b200_verify_scratch_bytes() bytes. */
+ * may then be NULL).  `scratch` is caller-owned device memory of ds41_b200_verify_scratch_bytes() bytes (16-byte
+ * aligned); with at least 48 bytes per logits row the slower cluster-only path is used instead of the streaming one. */
 typedef struct ds41_b200_verify_args {
   uint32_t struct_bytes;
   int32_t sequences, drafts, vocab;
@@ -125,6 +132,7 @@ typedef struct ds41_b200_verify_args {
   size_t scratch_bytes;
 } ds41_b200_verify_args;
 size_t ds41_b200_verify_scratch_bytes(int sequences, int drafts);
+size_t ds41_b200_verify_scratch_bytes_for(int sequences, int drafts, int vocab);
 int ds41_b200_verify_logits(const ds41_b200_verify_args *args, cudaStream_t stream);
 
 /* Same verification for callers that cannot provide or allocate scratch memory (an engine running on a fixed
@@ -140,34 +148,39 @@ int ds41_b200_verify_logits_static(const ds41_b200_verify_args *args, cudaStream
 /* ---- vocabulary-sharded sampling (several GPUs, one rank per GPU) -----------------------------------------------
  * No counterpart in the reference (single GPU, no collectives: scripts/run.py:228).  Rank r owns the logits of the
  * contiguous id range [vocab_offset, vocab_offset + vocab_local) (e.g. its slice of the head's weight rows).
- *   1. every rank: ds41_b200_shard_candidates -> one ds41_b200_shard_row per row (544 bytes);
- *   2. caller: all-gather of the records into `gathered` [ranks][rows] (ncclAllGather on the same stream);
- *   3. every rank: ds41_b200_shard_combine -> the same token ids on every rank.
- * A row whose nucleus may extend beyond some rank's 64 candidates gets status DS41_B200_ROW_NOT_COVERED and
- * token -1; the caller must then sample that row from its full logits (ds41_b200_sample_logits).  top_p = 1 is
- * therefore only covered when every shard holds at most 64 allowed ids. */
+ *   1. every rank: ds41_b200_shard_candidates -> `chunks` records of 544 bytes per row (one per 8192 ids; pass the
+ *      same `chunks` >= ds41_b200_shard_chunks(largest vocab_local) on every rank so that the records line up);
+ *   2. caller: all-gather of the records into `gathered` [ranks][rows][chunks] (ncclAllGather on the same stream);
+ *   3. every rank: ds41_b200_shard_combine -> the same token ids on every rank (ranks * chunks <= 17).
+ * A row whose surviving ids may extend beyond some chunk's 64 candidates gets status DS41_B200_ROW_NOT_COVERED and
+ * token -1; the caller must then sample that row from its full logits (ds41_b200_sample_logits).  top_p = 1 without
+ * top_k is therefore only covered for tiny vocabularies; top_k must be <= 64. */
 #define DS41_B200_SHARD_CANDIDATES 64
 typedef struct ds41_b200_shard_row {
   double z;
   float max_logit;
   int32_t argmax, count, status;
-  int32_t complete; /* 1: cand[] holds every allowed id of the shard */
+  int32_t complete; /* 1: cand[] holds every id of the chunk */
+  float z_err;
   struct { float y; int32_t id; } cand[DS41_B200_SHARD_CANDIDATES];
 } ds41_b200_shard_row;
 typedef struct ds41_b200_shard_args {
   uint32_t struct_bytes;
   int32_t rows, vocab_local, vocab_offset;
+  int32_t chunks;           /* records per row; 0 = ds41_b200_shard_chunks(vocab_local) */
   const float *logits;      /* [rows, logits_stride], this rank's id range */
   int64_t logits_stride;
   double temperature;
-  ds41_b200_shard_row *out; /* [rows] */
+  ds41_b200_shard_row *out; /* [rows][chunks] */
 } ds41_b200_shard_args;
+int ds41_b200_shard_chunks(int vocab_local);
 int ds41_b200_shard_candidates(const ds41_b200_shard_args *args, cudaStream_t stream);
 typedef struct ds41_b200_shard_combine_args {
   uint32_t struct_bytes;
-  int32_t rows, ranks, vocab;            /* ranks <= 8, vocab = full vocabulary */
-  const ds41_b200_shard_row *gathered;   /* [ranks][rows] */
+  int32_t rows, ranks, chunks, vocab;    /* vocab = full vocabulary */
+  const ds41_b200_shard_row *gathered;   /* [ranks][rows][chunks] */
   double temperature, top_p;
+  int32_t top_k;                         /* 0 = off, else <= 64 */
   const uint64_t *seeds, *steps;         /* [rows] */
   uint32_t slot, purpose;
   int32_t *tokens, *status;              /* [rows] out */

@@ -13,8 +13,8 @@ import torch.multiprocessing as mp
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REC = np.dtype([("z", np.float64), ("max", np.float32), ("argmax", np.int32), ("count", np.int32),
-                ("status", np.int32), ("complete", np.int32), ("cand", [("y", np.float32), ("id", np.int32)], 64),
-                ("pad", np.int32)])  # the C struct is 8-byte aligned: 540 -> 544 bytes
+                ("status", np.int32), ("complete", np.int32), ("z_err", np.float32),
+                ("cand", [("y", np.float32), ("id", np.int32)], 64)])
 
 
 def test_shard_plan():
