@@ -113,6 +113,18 @@ def zipf_gauss_logits(torch, device, rows, seed, sigma=3.0):
     return out
 
 
+def capture(torch, fn):
+    """Records fn() (kernel launches on static buffers) into a CUDA graph; the library's entry points only enqueue
+    work on the current stream, so they are capture-safe (the reference captures its head the same way:
+    engine/src/hotpath/batch.inc:484 bgraph("head"))."""
+    fn()  # warm-up outside capture: one-time function attributes, tensor-map encoder lookup
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    return g
+
+
 class HeadSample:
     """cfg2 / cfg5: hidden -> quantise -> FP8 head (this rank's vocabulary slice) -> sampler."""
 
@@ -142,6 +154,7 @@ class HeadSample:
         self.alg_bytes = self.vn * HIDDEN + self.ws.numel() * 4 + batch * HIDDEN + batch * 32 * 4
         self.alg_flops = 2.0 * batch * self.vn * HIDDEN
         self.bound = "hbm" if batch <= 128 else "tensor"
+        self.graph = None
         self.sharded = None
         if world > 1:
             self.sharded = import_module("ds41_b200.sharded").ShardedSampler(pkg, torch, device, batch, self.v0, self.vn,
@@ -161,11 +174,23 @@ class HeadSample:
         if self.sharded:
             self.sharded.sample(self.logits, self.seeds, self.steps, self.tokens, self.status)
         else:
-            pkg.sample_logits(self.logits, self.t, self.top_p, self.seeds, self.steps, tokens=self.tokens, status=self.status)
+            pkg.sample_logits(self.logits, self.t, self.top_p, self.seeds, self.steps, tokens=self.tokens,
+                              status=self.status, scratch=None)  # flat logits (random head): cluster kernel directly
+
+    def graph_step(self, i, from_host=False):
+        """The same step replayed from a CUDA graph over the static `hidden` buffer (single GPU only: the sharded
+        path checks a device flag on the host every step)."""
+        if self.sharded:
+            return self.step(i, self.hidden if from_host else None)
+        if self.graph is None:
+            self.graph = capture(self.torch, lambda: self.step(0, self.hidden))
+        if not from_host:
+            self.hidden.copy_(self.ring[i % len(self.ring)], non_blocking=True)
+        self.graph.replay()
 
     def e2e_step(self, i):
         self.hidden.copy_(self.host_ring[i % len(self.host_ring)], non_blocking=True)
-        self.step(i, self.hidden)
+        self.graph_step(i, from_host=True)
         self.tokens_host.copy_(self.tokens, non_blocking=True)
         self.torch.cuda.current_stream().synchronize()
         return self.tokens_host
@@ -199,6 +224,7 @@ class VerifyWorkload:
         self.status = torch.empty(seqs, dtype=torch.int32, device=device)
         self.results_host = torch.empty(seqs * 40, dtype=torch.uint8).pin_memory()
         self.host_sets = None
+        self.graphs = {}
         self.units = seqs  # one verified transaction per sequence; emitted tokens are reported separately
         self.launches_per_step = 3
         self.h2d = (seqs * (2 * drafts + 1)) * VOCAB * 4 + seqs * drafts * 4
@@ -217,6 +243,14 @@ class VerifyWorkload:
         if ev:
             ev[1].record()
 
+    def graph_step(self, i, from_host=False):
+        key = "host" if from_host else i % len(self.sets)
+        if key not in self.graphs:
+            s0 = self.sets[0]
+            inputs = self.dev_in + (s0[3], s0[4]) if from_host else self.sets[key]
+            self.graphs[key] = capture(self.torch, lambda: self.step(0, inputs))
+        self.graphs[key].replay()
+
     def e2e_step(self, i):
         torch = self.torch
         if self.host_sets is None:
@@ -224,8 +258,7 @@ class VerifyWorkload:
             self.dev_in = tuple(torch.empty_like(t) for t in self.sets[0][:3])
         for d, h in zip(self.dev_in, self.host_sets[i % len(self.host_sets)]):
             d.copy_(h, non_blocking=True)
-        s = self.sets[i % len(self.sets)]
-        self.step(i, self.dev_in + (s[3], s[4]))
+        self.graph_step(i, from_host=True)
         self.results_host.copy_(self.results, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return self.results_host
@@ -261,6 +294,7 @@ class PenaltyWorkload:
         self.status = torch.empty(batch, dtype=torch.int32, device=device)
         self.tokens_host = torch.empty(batch, dtype=torch.int32).pin_memory()
         self.host = None
+        self.graphs = {}
         self.units = batch
         self.launches_per_step = 1
         self.h2d = batch * (VOCAB * 4 + 32768 * 4 + VOCAB // 8)
@@ -280,6 +314,13 @@ class PenaltyWorkload:
         if ev:
             ev[1].record()
 
+    def graph_step(self, i, from_host=False):
+        key = "host" if from_host else "dev"
+        if key not in self.graphs:
+            inputs = self.dev_in if from_host else None
+            self.graphs[key] = capture(self.torch, lambda: self.step(0, inputs))
+        self.graphs[key].replay()
+
     def e2e_step(self, i):
         torch = self.torch
         if self.host is None:
@@ -287,7 +328,7 @@ class PenaltyWorkload:
             self.dev_in = tuple(torch.empty_like(t) for t in (self.logits, self.history, self.mask))
         for d, h in zip(self.dev_in, self.host):
             d.copy_(h, non_blocking=True)
-        self.step(i, self.dev_in)
+        self.graph_step(i, from_host=True)
         self.tokens_host.copy_(self.tokens, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return self.tokens_host
@@ -446,11 +487,10 @@ def main():
 
     warm = max(3, args.warmup)
     for i in range(warm):
-        wl.step(i)
+        wl.graph_step(i)
     barrier()
     wl.check()
-    # ---- device-resident timing: K steps between two events, plus an event pair around the dominant kernel
-    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    # ---- device-resident timing: K steps (CUDA-graph replays) between two events
     clocks = ClockSampler(local)
     if rank == 0:
         clocks.start()
@@ -458,10 +498,16 @@ def main():
     barrier()
     t0.record()
     for i in range(args.steps):
-        wl.step(i, ev=pairs[i])
+        wl.graph_step(i)
     t1.record()
     barrier()
     ms = t0.elapsed_time(t1)
+    # ---- the dominant kernel on its own: an event pair around it in K more steps launched eagerly on the same stream
+    # (events cannot be read back from inside a replayed graph)
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for i in range(args.steps):
+        wl.step(i, ev=pairs[i])
+    barrier()
     kernel_ms = sum(a.elapsed_time(b) for a, b in pairs) / args.steps
     # ---- end to end: inputs from pinned host memory, result read back every step
     e2e_steps = args.steps
@@ -500,7 +546,8 @@ def main():
                 "data": "synthetic", "config": workload_config(name, world), "clocks": clock_info,
                 "e2e": {"value": units * e2e_steps / e2e_s, "unit": "sequences/s" if name.startswith("cfg3") else "tokens/s",
                         "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_s / e2e_steps * 1e3},
-                "gpu_launches": wl.launches_per_step * args.steps, "roofline": roof}
+                "gpu_launches": wl.launches_per_step * args.steps, "roofline": roof,
+                "launch": "one CUDA graph replay per step" if world == 1 else "eager launches (host checks the coverage flag every step)"}
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline(name)
         print(json.dumps(line))

@@ -321,7 +321,7 @@ __device__ CutResult find_cut(RowCtx &c, float max_logit, float first_width, int
   L.n = 1; L.lo[0] = 0.f; L.inv_w[0] = 1.f / first_width; L.bounded[0] = false; L.pick[0] = 0;
   CutResult out{};
   out.cut.y = -CUDART_INF_F; out.cut.id = -1;
-  const double rel_bound = 2.0 * (double(n_active) + 64.0) * kU;
+  const double rel_bound = 2.0 * (double(n_active) + 256.0) * kU;
   int count_before_level = 0;                // ids before the current level's range (exact)
   unsigned long long mass_before_level = 0;  // their fixed-point mass
   unsigned long long target_fix = 0;

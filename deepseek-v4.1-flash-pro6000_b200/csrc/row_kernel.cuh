@@ -3,6 +3,7 @@
 #pragma once
 #include "row_core.cuh"
 #include "row_fast.cuh"
+#include "row_wide.cuh"
 
 namespace ds41 {
 
@@ -173,7 +174,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
 
   // ---- effective logits, first maximum, allowed count
   int flags = (landed ? 0 : 8) | (bad_history ? 4 : 0);
-  float best = -CUDART_INF_F;
+  float best = -CUDART_INF_F, lowest = CUDART_INF_F;  // lowest: smallest finite effective logit
   int best_id = 0x7fffffff, allowed = 0;
   for (int it = 0; it < c.region; it += 32) {
     const int j = c.warp * c.region + it + c.lane;
@@ -194,13 +195,19 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
     if (ok) {
       ++allowed;
       if (x > best) { best = x; best_id = c.begin + j; }
+      if (x > -CUDART_INF_F) lowest = fminf(lowest, x);
     }
   }
   __syncthreads();
   {
     Slot mine{};
     block_argmax(c, best, best_id);
-    mine.f[0] = best; mine.i[0] = best_id;
+    {  // block minimum through the order-preserving integer image of -lowest
+      const int bits = __float_as_int(-lowest);
+      const int top = block_max(c, bits >= 0 ? bits : bits ^ 0x7fffffff);
+      lowest = -__int_as_float(top >= 0 ? top : top ^ 0x7fffffff);
+    }
+    mine.f[0] = best; mine.i[0] = best_id; mine.f[1] = lowest;
     mine.i[1] = block_or(c, flags);
     mine.i[2] = block_sum(c, allowed);
     const Slot *all = exchange(c, mine);
@@ -210,6 +217,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
       flags |= all[r].i[1];
       allowed += all[r].i[2];
     }
+    for (int r = 0; r < c.nranks; ++r) lowest = fminf(lowest, all[r].f[1]);
   }
   int status = 0;
   if (flags & 8) status = -5;
@@ -220,7 +228,10 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
 
   const float max_logit = best;
   const double t = a.temperature;
-  auto weight = [max_logit, t](float y) { return exp((double(y) - double(max_logit)) / t); };
+  // exp((y - max)/T) with the division replaced by a multiplication: the argument moves by at most one ulp, the
+  // value by |argument| * 2^-53 relative (< 100 u), which every comparison made on sums of these weights allows for
+  const double inv_t = t > 0 ? 1.0 / t : 0.0;
+  auto weight = [max_logit, inv_t](float y) { return exp((double(y) - double(max_logit)) * inv_t); };
   Cut cut{-CUDART_INF_F, -1};
   // value of local id j for the sums and the draw: exp weight of a survivor of the CURRENT cut, else 0
   auto value = [&cut, &c, s, weight](int j) {
@@ -231,7 +242,17 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
   double z = 0, e_kept = 0;
   int token = -1;
 
-  {
+  bool wide_done = false;
+  if (status == 0 && t != 0 && a.top_p < 1.0 && (a.top_k <= 0 || a.top_k >= allowed) && allowed > 2 * kListCap &&
+      lowest < max_logit) {
+    const WideOutcome w = wide_nucleus(c, max_logit, lowest, t, a.top_p, allowed);
+    if (w.applicable) {
+      wide_done = true;
+      cut = w.cut; kept = w.kept; z = w.z; e_kept = w.e_kept;
+      if (w.ambiguous) status |= 2;
+    }
+  }
+  if (!wide_done) {
     if (status == 0 && t != 0) {
       const double u = kMode == kModeSample ? philox_uniform(a.seeds[row], a.steps[row], a.slot, a.purpose) : 0.0;
       const FastOutcome f = fast_small_support(c, max_logit, t, allowed, a.top_k, a.top_p, u, kMode == kModeSample);
@@ -252,7 +273,9 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
       }
     }
   }
-  if (status == 0 && t == 0) {
+  if (wide_done) {
+    // cut, sums and region sums are in place
+  } else if (status == 0 && t == 0) {
     token = best_id;
     kept = 1; z = 1; e_kept = 1;
     cut.y = max_logit; cut.id = best_id;
@@ -286,13 +309,13 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
       for (int r = 0; r < c.nranks; ++r) z += all[r].d[0];
       e_kept = z;
     }
-    if (status >= 0 && kMode == kModeSample) {
-      const double u = philox_uniform(a.seeds[row], a.steps[row], a.slot, a.purpose);
-      int amb = 0;
-      double total;
-      token = draw_token(c, u, (2.0 * kept + 256.0) * kU, 0.0, value, &amb, &total);
-      if (amb) status |= 1;
-    }
+  }
+  if (status >= 0 && t != 0 && kMode == kModeSample) {
+    const double u = philox_uniform(a.seeds[row], a.steps[row], a.slot, a.purpose);
+    int amb = 0;
+    double total;
+    token = draw_token(c, u, (2.0 * kept + 512.0) * kU, 0.0, value, &amb, &total);
+    if (amb) status |= 1;
   }
   if (c.rank == 0 && c.tid == 0) {
     if (kMode == kModeSample) {

@@ -5,7 +5,6 @@
 #include "host_error.h"
 #include "stream.cuh"
 #include <cmath>
-#include <cstdlib>
 
 namespace ds41 {
 
@@ -13,18 +12,12 @@ static_assert(sizeof(ChunkRecord) == sizeof(ds41_b200_shard_row), "shard record 
 
 int chunks_for(int vocab) { return (vocab + kChunkIds - 1) / kChunkIds; }
 
-cudaError_t launch_chunks(const ChunkArgs &a0, int rows, cudaStream_t stream) {
-  ChunkArgs a = a0;
-  const char *dbg = getenv("DS41_CHUNK_STOP");
-  a.debug_stop = dbg ? atoi(dbg) : 0;
+cudaError_t launch_chunks(const ChunkArgs &a, int rows, cudaStream_t stream) {
   chunk_kernel<<<unsigned(rows) * unsigned(a.chunks), kChunkThreads, 0, stream>>>(a);
   return cudaGetLastError();
 }
 
-cudaError_t launch_combine(const CombineArgs &a0, bool stats, cudaStream_t stream) {
-  CombineArgs a = a0;
-  const char *dbg = getenv("DS41_COMBINE_STOP");
-  a.debug_stop = dbg ? atoi(dbg) : 0;
+cudaError_t launch_combine(const CombineArgs &a, bool stats, cudaStream_t stream) {
   static thread_local int configured = -1;
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);

@@ -83,7 +83,6 @@ __global__ void __launch_bounds__(kChunkThreads, 4) chunk_kernel(ChunkArgs a) {
     if (tid == 0) { out->status = -5; out->count = 0; out->complete = 0; out->z = 0; out->max_logit = 0; out->argmax = -1; out->z_err = 0.f; }
     return;
   }
-  if (a.debug_stop == 1) return;
   const int vecs = len >> 2, tail0 = vecs << 2;  // full vectors; ids tail0..len-1 (at most 3) are handled by scalar code
   const float4 *y4 = reinterpret_cast<const float4 *>(s.y);
 
@@ -127,7 +126,6 @@ __global__ void __launch_bounds__(kChunkThreads, 4) chunk_kernel(ChunkArgs a) {
     }
     return;
   }
-  if (a.debug_stop == 2) return;
   const float m = best;
   // how far below the maximum do the first 64 ids reach?  The 256 per-thread maxima are a sample of the top of the
   // chunk: the smallest ladder distance that holds 64 of them holds at least 64 ids.
@@ -159,7 +157,6 @@ __global__ void __launch_bounds__(kChunkThreads, 4) chunk_kernel(ChunkArgs a) {
     if (lane == 0) atomicAdd(&s.acc_d[0], wa);
   }
   __syncthreads();  // also publishes ladder_count
-  if (a.debug_stop == 3) return;
   float reach = 32.f;
   {
     const float ladder[12] = {0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f, 8.f, 12.f, 16.f, 24.f, 32.f};
@@ -199,7 +196,6 @@ __global__ void __launch_bounds__(kChunkThreads, 4) chunk_kernel(ChunkArgs a) {
     if (y > near_above) atomicAdd(&s.bins[min(kFineBins - 1, int((m - y) * bin_scale))], 1);
   }
   __syncthreads();
-  if (a.debug_stop == 4) return;
   // ---- bin that holds the 64th id: block-wide inclusive scan of the 256 bins (one bin per thread)
   {
     const int v = s.bins[tid];
@@ -328,7 +324,6 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineArgs a)
     }
     return;
   }
-  if (a.debug_stop == 1) return;
   if (tid < nrec) s.hw[tid] = s.hz[tid] > 0 ? exp((double(s.hmax[tid]) - double(m)) / t) : 0.0;
   if (tid == 0) {
     s.base[0] = 0;
@@ -384,7 +379,6 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineArgs a)
     if (lane == 0) s.i_out[5] = found < 0 ? kCombineBins : min(kCombineBins - 2, found + 2);
   }
   __syncthreads();
-  if (a.debug_stop == 2) return;
   const int last_bin = s.i_out[5];  // candidates in bins <= last_bin are ranked exactly (all of them if no crossing)
   for (int q = tid; q < n; q += kCombineThreads) {
     const float d = m - s.cy[q];
@@ -405,11 +399,12 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineArgs a)
     int pos = 0;
     for (int k = 0; k < nf; ++k) pos += (s.fy[k] > yi || (s.fy[k] == yi && s.fid[k] < idi)) ? 1 : 0;
     s.sy[pos] = yi; s.sid[pos] = idi;
-    s.se[pos] = exp((double(yi) - double(m)) / t);
+    const double e = exp((double(yi) - double(m)) / t);
+    s.se[pos] = e;
+    s.sp[pos] = e / z;  // p = e/z for the top-p walk (count mode recomputes it with its own normaliser)
     atomicMax(&s.worst[s.frec[i]], pos);  // worst position among this record's ranked candidates
   }
   __syncthreads();
-  if (a.debug_stop == 3) return;
   // ---- thread 0: who enters, normaliser, top-p prefix (the reference's loop), coverage
   if (tid == 0) {
     int st = 0, entered = nf, kept = 0;
@@ -436,20 +431,21 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineArgs a)
     }
     kept = entered;
     if (!(a.top_p < 1.0)) {
-      for (int i = 0; i < entered; ++i) s.sp[i] = s.se[i] / zz;
+      if (count_mode)
+        for (int i = 0; i < entered; ++i) s.sp[i] = s.se[i] / zz;
       if (!count_mode) {  // top_p = 1 without top-k keeps every id: only covered if every record is complete
         if (!filtered_all) covered = false;
         for (int r = 0; r < nrec; ++r) covered = covered && s.complete[r];
       }
     } else {
+      if (count_mode)
+        for (int i = 0; i < entered; ++i) s.sp[i] = s.se[i] / zz;
       mass = 0;
       int k = 0;
       double prev = 0;
       do {
         prev = mass;
-        const double p = s.se[k] / zz;
-        s.sp[k++] = p;
-        mass += p;
+        mass += s.sp[k++];
       } while (k < entered && mass < a.top_p);
       kept = k;
       if (!count_mode) {
@@ -461,7 +457,6 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineArgs a)
           if (!(mass < a.top_p * (1.0 - rel))) st |= 2;
         } else if (mass < a.top_p * (1.0 + rel) || prev >= a.top_p * (1.0 - rel)) st |= 2;
       }
-      for (int i = 0; i < kept; ++i) s.sp[i] /= mass;
     }
     // a record that did not send all of its ids must have its WORST candidate outside the surviving prefix (ids it
     // did not send are worse still).  A record with a candidate beyond the ranked bins is fine: that one is outside.
@@ -473,10 +468,9 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineArgs a)
     double e_kept = 0;
     for (int i = 0; i < kept; ++i) e_kept += s.se[i];
     s.i_out[0] = covered ? st : kNotCovered; s.i_out[1] = kept; s.i_out[2] = count_mode ? a.top_k : a.vocab;
-    s.d_out[0] = zz; s.d_out[1] = e_kept;
+    s.d_out[0] = zz; s.d_out[1] = e_kept; s.d_out[2] = mass;
   }
   __syncthreads();
-  if (a.debug_stop == 4) return;
   status = s.i_out[0];
   const int kept = s.i_out[1];
   if (status == kNotCovered) {
@@ -496,10 +490,12 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineArgs a)
     return;
   }
   // ---- survivors in id order, then the reference's draw
+  const double kept_mass = s.d_out[2];
   for (int i = tid; i < kept; i += kCombineThreads) {
     int pos = 0;
     for (int k = 0; k < kept; ++k) pos += s.sid[k] < s.sid[i] ? 1 : 0;
     s.by_id[pos] = i;
+    if (a.top_p < 1.0) s.sp[i] /= kept_mass;  // p / mass (sampling.cpp:36), one id per thread
   }
   __syncthreads();
   if (tid == 0) {

@@ -46,7 +46,6 @@ struct ChunkArgs {
   int vocab_local, id_offset, chunks;  // chunks per row (>= ceil(vocab_local/kChunkIds); extra chunks are empty)
   double temperature;
   ChunkRecord *out;  // [rows][chunks]
-  int debug_stop;
 };
 
 enum CombineMode { kCombineDraw = 0, kCombineStats = 1 };
@@ -60,7 +59,6 @@ struct CombineArgs {
   uint32_t slot, purpose;
   int32_t *tokens, *status;
   RowStats *stats;
-  int debug_stop;
 };
 
 

@@ -38,12 +38,12 @@ struct VerifyArgs {
 struct Measure {  // one row's probability measure: P(id) = survives ? exp((x-max)/T) / e_kept : 0
   const float *x;
   RowStats st;
-  double t;
+  double inv_t, inv_kept;  // 1/T and 1/e_kept: multiplications instead of divisions (a few ulp, inside bound())
   __device__ __forceinline__ double at(int id) const {
     const float y = __ldg(x + id);
-    return survives(y, id, st.cut) ? exp((double(y) - double(st.max_logit)) / t) / st.e_kept : 0.0;
+    return survives(y, id, st.cut) ? exp((double(y) - double(st.max_logit)) * inv_t) * inv_kept : 0.0;
   }
-  __device__ __forceinline__ double bound() const { return 2.0 * (double(st.kept) + 64.0) * kU; }
+  __device__ __forceinline__ double bound() const { return 2.0 * (double(st.kept) + 256.0) * kU; }
 };
 
 __global__ void __launch_bounds__(kThreads, 2) verify_kernel(VerifyArgs a) {
@@ -71,13 +71,15 @@ __global__ void __launch_bounds__(kThreads, 2) verify_kernel(VerifyArgs a) {
   for (int k = 0; k < D && status >= 0 && !r.rejected; ++k) {
     const int d = a.ids[size_t(seq) * D + k];
     if (d < 0 || d >= a.vocab) { status = -6; break; }  // checked only when the position is reached (sampling.cpp:44)
-    Measure P{a.target + (size_t(seq) * (D + 1) + k) * a.vocab, a.pstats[size_t(seq) * (D + 1) + k], a.temperature};
+    const RowStats ps = a.pstats[size_t(seq) * (D + 1) + k];
+    Measure P{a.target + (size_t(seq) * (D + 1) + k) * a.vocab, ps, greedy ? 0.0 : 1.0 / a.temperature, 1.0 / ps.e_kept};
     bool accept;
     if (greedy) {
       accept = d == P.st.argmax;
       if (!accept) { r.tokens[r.emitted++] = P.st.argmax; r.rejected = 1; }
     } else {
-      Measure Q{a.draft + (size_t(seq) * D + k) * a.vocab, a.qstats[size_t(seq) * D + k], a.temperature};
+      const RowStats qs = a.qstats[size_t(seq) * D + k];
+      Measure Q{a.draft + (size_t(seq) * D + k) * a.vocab, qs, 1.0 / a.temperature, 1.0 / qs.e_kept};
       const double pd = P.at(d), qd = Q.at(d);
       if (!(qd > 0)) { status = -6; break; }
       const double ratio = fmin(1.0, pd / qd);
@@ -102,7 +104,8 @@ __global__ void __launch_bounds__(kThreads, 2) verify_kernel(VerifyArgs a) {
     if (accept) { r.tokens[r.emitted++] = d; ++r.accepted_drafts; }
   }
   if (status >= 0 && !r.rejected) {
-    Measure P{a.target + (size_t(seq) * (D + 1) + D) * a.vocab, a.pstats[size_t(seq) * (D + 1) + D], a.temperature};
+    const RowStats ps = a.pstats[size_t(seq) * (D + 1) + D];
+    Measure P{a.target + (size_t(seq) * (D + 1) + D) * a.vocab, ps, greedy ? 0.0 : 1.0 / a.temperature, 1.0 / ps.e_kept};
     if (greedy) {
       r.tokens[r.emitted++] = P.st.argmax;
     } else {
