@@ -8,7 +8,9 @@ One "step" is one pass of the hot path over one batch of synthetic input (BASELI
   cfg3_verify     32 sequences x (1 target + 2 draft) logits rows -> accept / residual / bonus
   cfg4_penalties  256 rows: 32K-token history penalties + bitmask + top-k 50 + top-p 0.9, T=0.8
   cfg5_b1024      B=1024, FP8 head + sampler; with --gpus N>1 the vocabulary is sharded over the ranks
-Default: cfg2_b64 on one GPU, cfg5_b1024 (vocabulary sharded, one NCCL all-gather per step) on several.
+Default at every N: cfg5_b1024, the B=1024 head + top-p job (on one GPU the unsharded job, i.e. the cfg2 recipe at the
+batch the multi-GPU target is quoted on), so that N=1,2,4,8 form one strong-scaling series; the other workloads are
+selected with --workload.
 Prints ONE JSON line (rank 0).  Weights stay resident in HBM (as in the reference engine); `value` is measured with the
 step's inputs already on the device, `e2e` with the hidden states copied from pinned host memory and the token ids
 read back every step.  `--impl reference` times the reference's own CPU sampling rule on the host cores.
@@ -30,7 +32,15 @@ VOCAB, HIDDEN = 129280, 4096
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised
 # under profiles/ (None = not captured yet)
-NCU_TRAFFIC = {}
+NCU_TRAFFIC = {
+    # head_fp8_kernel<64,1>, cfg2_b64: 531.43 MB read + 35.58 MB written (profiles/head_fp8_kernel_cfg2_b64.md)
+    ("cfg2_b64", "head_fp8_kernel"): 567.0e6,
+    # row_kernel<0>, cfg2_b64: 33.19 MB read + 256 B written (profiles/row_kernel_cfg2_b64.md)
+    ("cfg2_b64", "row_kernel"): 33.19e6,
+    # cfg5_b1024 is too large to capture with --set full under the capture-size rule; the row kernel's traffic grows in
+    # proportion to the rows (each row's logits are read once), so the cfg2_b64 capture is scaled by 1024 / 64
+    ("cfg5_b1024", "row_kernel"): 33.19e6 * 16,
+}
 
 
 def peaks():
@@ -128,7 +138,7 @@ def capture(torch, fn):
 class HeadSample:
     """cfg2 / cfg5: hidden -> quantise -> FP8 head (this rank's vocabulary slice) -> sampler."""
 
-    def __init__(self, pkg, torch, device, batch, rank, world, temperature=0.6, top_p=0.95):
+    def __init__(self, pkg, torch, device, batch, rank, world, temperature=0.6, top_p=0.95, strategy="rows"):
         self.pkg, self.torch, self.device, self.B, self.rank, self.world = pkg, torch, device, batch, rank, world
         self.t, self.top_p = temperature, top_p
         from importlib import import_module
@@ -150,32 +160,55 @@ class HeadSample:
         self.units = batch
         self.launches_per_step = 3
         self.h2d, self.d2h = batch * HIDDEN * 2, batch * 4
-        self.kernel = "head_fp8_kernel"
-        self.alg_bytes = self.vn * HIDDEN + self.ws.numel() * 4 + batch * HIDDEN + batch * 32 * 4
-        self.alg_flops = 2.0 * batch * self.vn * HIDDEN
-        self.bound = "hbm" if batch <= 128 else "tensor"
+        # the two kernels that can dominate a step, each timed with its own event pair
+        head_bytes = self.vn * HIDDEN + self.ws.numel() * 4 + batch * HIDDEN + batch * 32 * 4 + batch * self.vn * 4
+        my_rows = -(-batch // world)
+        self.kernels = {
+            "head_fp8_kernel": {"bound": "hbm" if batch <= 128 else "tensor", "bytes": head_bytes,
+                                "flops": 2.0 * batch * self.vn * HIDDEN},
+            "row_kernel": {"bound": "hbm", "bytes": my_rows * VOCAB * 4 + my_rows * 24, "flops": 0.0},
+        }
         self.graph = None
         self.sharded = None
         if world > 1:
-            self.sharded = import_module("ds41_b200.sharded").ShardedSampler(pkg, torch, device, batch, self.v0, self.vn,
-                                                                           VOCAB, temperature, top_p)
-            self.launches_per_step = 2 + self.sharded.launches_per_step
+            self.sharded = import_module("ds41_b200.sharded").ShardedDecodeTail(pkg, device, batch, self.v0, self.vn,
+                                                                              VOCAB, temperature, top_p, strategy)
+            self.launches_per_step = 3 if strategy == "rows" else 4
 
     def step(self, i, hidden=None, ev=None):
         pkg = self.pkg
         x = self.ring[i % len(self.ring)] if hidden is None else hidden
         self.steps.add_(1)  # a fresh Philox step per decode step (spark.h:122-128)
         pkg.quantize_activations(x, self.a, self.a_scale)
+        if self.sharded:
+            # per-kernel events only in the "rows" exchange: head (with its peer stores) | one-word all-reduce | sampler
+            if ev and self.sharded.mode() == "rows":
+                exch = self.sharded.exchange
+                ev[0].record()
+                exch.head_scatter(self.a, self.a_scale, self.wq, self.ws, self.v0, self.flag)
+                ev[1].record()
+                exch.writers_done()
+                ev[2].record()
+                exch.sample_mine(self.t, self.top_p, self.seeds, self.steps, scratch=None)
+                ev[3].record()
+                exch.publish(self.tokens, self.status)
+                return
+            self.sharded.step(self.a, self.a_scale, self.wq, self.ws, self.seeds, self.steps, self.tokens, self.status,
+                              self.flag)
+            if ev:
+                for e in ev:
+                    e.record()
+            return
         if ev:
             ev[0].record()
         pkg.head_fp8(self.a, self.a_scale, self.wq, self.ws, self.logits, self.flag)
         if ev:
             ev[1].record()
-        if self.sharded:
-            self.sharded.sample(self.logits, self.seeds, self.steps, self.tokens, self.status)
-        else:
-            pkg.sample_logits(self.logits, self.t, self.top_p, self.seeds, self.steps, tokens=self.tokens,
-                              status=self.status, scratch=None)  # flat logits (random head): cluster kernel directly
+            ev[2].record()
+        pkg.sample_logits(self.logits, self.t, self.top_p, self.seeds, self.steps, tokens=self.tokens,
+                          status=self.status, scratch=None)  # flat logits (random head): cluster kernel directly
+        if ev:
+            ev[3].record()
 
     def graph_step(self, i, from_host=False):
         """The same step replayed from a CUDA graph over the static `hidden` buffer (single GPU only: the sharded
@@ -199,6 +232,21 @@ class HeadSample:
         assert self.flag.item() == 0, "head kernel reported a wait timeout"
         st = self.status.cpu().numpy()
         assert (st >= 0).all(), st
+
+    def check_against_single_gpu(self):
+        """Sharded run, rank 0: recompute the last step unsharded (all ranks' weight slices, one GPU) and compare the
+        token ids: the sharded path must give the 1-GPU path's tokens."""
+        torch, pkg = self.torch, self.pkg
+        plan = __import__("ds41_b200.sharded", fromlist=["shard_plan"]).shard_plan(VOCAB, self.world)
+        parts = [make_weights(torch, self.device, n, 1234 + r) for r, (_, n) in enumerate(plan)]
+        wq = torch.cat([p[0] for p in parts]); ws = torch.cat([p[1] for p in parts])
+        logits = torch.empty((self.B, VOCAB), dtype=torch.float32, device=self.device)
+        pkg.head_fp8(self.a, self.a_scale, wq, ws, logits, self.flag)
+        tok, st = pkg.sample_logits(logits, self.t, self.top_p, self.seeds, self.steps, scratch=None)
+        torch.cuda.synchronize()
+        same = bool((tok == self.tokens).all().item())
+        assert same, "sharded tokens differ from the single-GPU path"
+        return same
 
 
 class VerifyWorkload:
@@ -229,10 +277,7 @@ class VerifyWorkload:
         self.launches_per_step = 3
         self.h2d = (seqs * (2 * drafts + 1)) * VOCAB * 4 + seqs * drafts * 4
         self.d2h = seqs * 40
-        self.kernel = "row_kernel"
-        self.alg_bytes = seqs * (2 * drafts + 1) * VOCAB * 4
-        self.alg_flops = 0.0
-        self.bound = "hbm"
+        self.kernels = {"row_kernel": {"bound": "hbm", "bytes": seqs * (2 * drafts + 1) * VOCAB * 4, "flops": 0.0}}
 
     def step(self, i, inputs=None, ev=None):
         target, draft, ids, seeds, steps = inputs or self.sets[i % len(self.sets)]
@@ -299,10 +344,7 @@ class PenaltyWorkload:
         self.launches_per_step = 1
         self.h2d = batch * (VOCAB * 4 + 32768 * 4 + VOCAB // 8)
         self.d2h = batch * 4
-        self.kernel = "row_kernel"
-        self.alg_bytes = batch * (VOCAB * 4 + 32768 * 4 + VOCAB // 8)
-        self.alg_flops = 0.0
-        self.bound = "hbm"
+        self.kernels = {"row_kernel": {"bound": "hbm", "bytes": batch * (VOCAB * 4 + 32768 * 4 + VOCAB // 8), "flops": 0.0}}
 
     def step(self, i, inputs=None, ev=None):
         logits, history, mask = inputs or (self.logits, self.history, self.mask)
@@ -381,7 +423,8 @@ def cpu_baseline(workload_name, budget_rows=None):
         return {"value": rows / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
                 "sample": f"{rows} rows; penalties/bitmask/top-k have no reference code, so this is the repository's CPU rule"}
     rows = budget_rows or max(64, 4 * cores)
-    x = orc.gen_logits(2, min(rows, 64), VOCAB)
+    # logits with the distribution the FP8 head produces on this recipe: N(0, (0.02 * sqrt(4096))^2) = N(0, 1.28^2)
+    x = orc.gen_normal(2, 0, (min(rows, 64), VOCAB), 1.28)
     x = np.concatenate([x] * ((rows + x.shape[0] - 1) // x.shape[0]))[:rows]
     t0 = time.perf_counter()
     if ref.available:
@@ -395,17 +438,23 @@ def cpu_baseline(workload_name, budget_rows=None):
         kind = "port"
     dt = time.perf_counter() - t0
     return {"value": rows / dt, "unit": "tokens/s", "cores": cores, "kind": kind,
-            "sample": f"{rows} logits rows [129280] through probabilities(T=0.6, top_p=0.95) + sample; the reference has "
-                      "no CPU LM head, so the head is not in this figure"}
+            "sample": f"{rows} logits rows [129280] ~ N(0,1.28^2) (the head's output distribution) through "
+                      "probabilities(T=0.6, top_p=0.95) + sample; the reference has no CPU LM head, so the head is not "
+                      "in this figure"}
 
 
-def workload_config(name, world):
+def workload_config(name, world, exchange=None):
     cfg = {"workload": name, "vocab": VOCAB, "data_recipe": "BASELINE.json configs, seeded synthetic"}
     if name.startswith("cfg2") or name.startswith("cfg5"):
         cfg.update({"hidden": HIDDEN, "batch": int(name.split("_b")[1]), "temperature": 0.6, "top_p": 0.95,
                     "weights": "e4m3 [129280,4096] + fp32 scale per 128x128, resident in HBM",
-                    "parallelism": "1 GPU" if world == 1 else f"vocab-sharded x{world} (128-row blocks), 1 NCCL all-gather/step",
+                    "parallelism": "1 GPU" if world == 1 else f"head vocab-sharded x{world} (128-row blocks), sampler row-sharded",
                     "l2": "529.5 MB of weights stream from HBM every step (> 126 MB L2); hidden states cycle over 16 buffers"})
+        if world > 1:
+            cfg["exchange"] = {"rows": "head epilogue stores each row's slice into the row owner's buffer (peer stores), "
+                                       "1-word all-reduce, all-gather of tokens",
+                               "candidates": "all-gather of 544-byte chunk records, replicated combine, uncovered rows "
+                                             "re-gathered", "auto": "candidates, rows when coverage fails"}[exchange]
     elif name.startswith("cfg3"):
         cfg.update({"sequences": 32, "drafts": 2, "temperature": 0.6, "top_p": 0.95,
                     "l2": "three 83 MB input sets cycled, so every step reads logits from HBM"})
@@ -432,7 +481,8 @@ def run_reference(args, rank, world):
     value = statistics.median(samples)
     base["value"] = value
     line = {"impl": "reference", "metric": metric_name(name), "value": value, "unit": base["unit"], "n_gpus": args.gpus,
-            "steps": len(samples), "warmup": 1, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+            "steps": len(samples), "warmup": 1, "ms_per_step": None, "higher_is_better": True,
+            "scaling": "strong" if name.startswith("cfg5") else "weak",
             "vs_baseline": None, "dtype": "f64", "data": "synthetic", "config": workload_config(name, 1),
             "cpu_baseline": base, "e2e": {"value": value, "unit": base["unit"], "h2d_bytes_per_step": 0,
                                           "d2h_bytes_per_step": 0}, "gpu_launches": 0}
@@ -451,12 +501,14 @@ def main():
     ap.add_argument("--workload", default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shard-exchange", default="rows", choices=["rows", "candidates", "auto"],
+                    help="N>1: how the vocabulary-sharded ranks exchange (see the package's sharded.py)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.workload is None:
-        args.workload = "cfg2_b64" if max(world, args.gpus) == 1 else "cfg5_b1024"
+        args.workload = "cfg5_b1024"  # the same job at every N, so that the per-N values form one scaling series
     if args.impl == "reference":
         return run_reference(args, rank, world)
 
@@ -472,7 +524,7 @@ def main():
     pkg = entry.load_package()
     name = args.workload
     if name.startswith("cfg2") or name.startswith("cfg5"):
-        wl = HeadSample(pkg, torch, device, int(name.split("_b")[1]), rank, world)
+        wl = HeadSample(pkg, torch, device, int(name.split("_b")[1]), rank, world, strategy=args.shard_exchange)
     elif name.startswith("cfg3"):
         wl = VerifyWorkload(pkg, torch, device)
     elif name.startswith("cfg4"):
@@ -502,13 +554,16 @@ def main():
     t1.record()
     barrier()
     ms = t0.elapsed_time(t1)
-    # ---- the dominant kernel on its own: an event pair around it in K more steps launched eagerly on the same stream
-    # (events cannot be read back from inside a replayed graph)
-    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    # ---- the kernels that can dominate, each on its own: event pairs around them in K more steps launched eagerly on
+    # the same stream (events cannot be read back from inside a replayed graph); the slowest one is the roofline's
+    names = list(wl.kernels)
+    quads = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     for i in range(args.steps):
-        wl.step(i, ev=pairs[i])
+        wl.step(i, ev=quads[i])
     barrier()
-    kernel_ms = sum(a.elapsed_time(b) for a, b in pairs) / args.steps
+    kernel_times = [sum(q[0].elapsed_time(q[1]) for q in quads) / args.steps]
+    if len(names) > 1:
+        kernel_times.append(sum(q[2].elapsed_time(q[3]) for q in quads) / args.steps)
     # ---- end to end: inputs from pinned host memory, result read back every step
     e2e_steps = args.steps
     for i in range(3):
@@ -521,33 +576,39 @@ def main():
     e2e_s = time.perf_counter() - w0
     clock_info = clocks.stop() if rank == 0 else None
     wl.check()
+    same_as_single = wl.check_against_single_gpu() if (world > 1 and rank == 0 and hasattr(wl, "check_against_single_gpu")) else None
     if world > 1:
-        t = torch.tensor([ms, e2e_s, kernel_ms], device=device, dtype=torch.float64)
+        t = torch.tensor([ms, e2e_s] + kernel_times, device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_s, kernel_ms = t.tolist()
+        ms, e2e_s, kernel_times = t[0].item(), t[1].item(), t[2:].tolist()
     if rank == 0:
         pk = peaks()
         units = wl.units
-        if wl.bound == "hbm":
-            achieved = wl.alg_bytes / (kernel_ms * 1e-3) / 1e9
-            roof = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                    "frac": achieved / pk["hbm_gbs"]}
-        else:
-            achieved = wl.alg_flops / (kernel_ms * 1e-3) / 1e12
-            roof = {"bound": "tensor", "achieved": achieved, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
-                    "frac": achieved / pk["bf16_tflops"]}
-        roof.update({"traffic": NCU_TRAFFIC.get(name), "kernel": wl.kernel, "kernel_ms": kernel_ms,
-                     "peak_source": pk["source"], "algorithmic_per_launch": wl.alg_bytes if wl.bound == "hbm" else wl.alg_flops})
+        per_kernel = []
+        for kname, kms in zip(names, kernel_times):
+            k = wl.kernels[kname]
+            if k["bound"] == "hbm":
+                achieved, peak, unit, alg = k["bytes"] / (kms * 1e-3) / 1e9, pk["hbm_gbs"], "GB/s", k["bytes"]
+            else:
+                achieved, peak, unit, alg = k["flops"] / (kms * 1e-3) / 1e12, pk["bf16_tflops"], "TFLOP/s", k["flops"]
+            per_kernel.append({"bound": k["bound"], "achieved": achieved, "peak": peak, "unit": unit,
+                               "frac": achieved / peak, "traffic": NCU_TRAFFIC.get((name, kname)), "kernel": kname,
+                               "kernel_ms": kms, "peak_source": pk["source"], "algorithmic_per_launch": alg})
+        per_kernel.sort(key=lambda k: -k["kernel_ms"])
+        roof = dict(per_kernel[0])
+        roof["other_kernels"] = per_kernel[1:]
         line = {"metric": metric_name(name), "value": units * args.steps / (ms * 1e-3),
                 "unit": "sequences/s" if name.startswith("cfg3") else "tokens/s", "n_gpus": world, "steps": args.steps,
                 "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True,
-                "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+                "scaling": "strong" if name.startswith("cfg5") else "weak", "vs_baseline": None,
                 "dtype": "e4m3 x e4m3 -> f32 (head), f32 logits / f64 sampler" if hasattr(wl, "wq") else "f32 logits, f64 sums",
-                "data": "synthetic", "config": workload_config(name, world), "clocks": clock_info,
+                "data": "synthetic", "config": workload_config(name, world, args.shard_exchange), "clocks": clock_info,
                 "e2e": {"value": units * e2e_steps / e2e_s, "unit": "sequences/s" if name.startswith("cfg3") else "tokens/s",
                         "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_s / e2e_steps * 1e3},
                 "gpu_launches": wl.launches_per_step * args.steps, "roofline": roof,
                 "launch": "one CUDA graph replay per step" if world == 1 else "eager launches (host checks the coverage flag every step)"}
+        if same_as_single is not None:
+            line["tokens_equal_single_gpu_path"] = same_as_single
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline(name)
         print(json.dumps(line))

@@ -123,6 +123,7 @@ struct HeadSmem {
   static constexpr int kStages = (200 * 1024 - 32 * kCols * 4) / kStageBytes > 12 ? 12 : (200 * 1024 - 32 * kCols * 4) / kStageBytes;
 };
 
+constexpr int kMaxOwners = 8;
 struct HeadArgs {
   const float *a_scale;  // [M, K/128]
   const float *w_scale;  // [ceil(N/128), K/128]
@@ -130,6 +131,11 @@ struct HeadArgs {
   long long ldl;
   int M, N, K;
   int *error_flag;       // device word, raised on a wait timeout (may be null)
+  // Row-scattered output (vocabulary-sharded head): batch row m goes to owner m / rows_per_owner, into
+  // owner_base[owner] + (m % rows_per_owner) * ldl + col_offset + n.  The bases may be peer GPUs' memory; the epilogue
+  // writes them with plain stores, so the vocabulary-to-row transposition rides on the GEMM.  rows_per_owner == 0: off.
+  float *owner_base[kMaxOwners];
+  int rows_per_owner, col_offset;
 };
 
 // kGroups epilogue warpgroups of 4 warps split the batch columns between them.
@@ -275,7 +281,14 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
           for (int c = 0; c < kMyCols; ++c) {
             const int m = bt * kCols + col0 + c;
-            if (m < p.M) p.logits[size_t(m) * p.ldl + n] = sum[c];
+            if (m < p.M) {
+              if (p.rows_per_owner == 0) {
+                p.logits[size_t(m) * p.ldl + n] = sum[c];
+              } else {
+                const int owner = m / p.rows_per_owner;
+                p.owner_base[owner][size_t(m - owner * p.rows_per_owner) * p.ldl + p.col_offset + n] = sum[c];
+              }
+            }
           }
         }
       }
@@ -376,12 +389,47 @@ extern "C" int ds41_b200_quantize_activations(const void *x_bf16, void *a_e4m3, 
   return int(cudaGetLastError());
 }
 
+namespace {
+int run_head(const void *a_e4m3, const float *a_scale, const void *w_e4m3, const float *w_scale, HeadArgs p,
+             cudaStream_t stream);
+}
+
 extern "C" int ds41_b200_head_fp8(const void *a_e4m3, const float *a_scale, const void *w_e4m3, const float *w_scale,
                                   float *logits, int64_t logits_stride, int M, int N, int K, int *error_flag,
                                   cudaStream_t stream) {
   if (!a_e4m3 || !a_scale || !w_e4m3 || !w_scale || !logits || M < 1 || N < 1 || K < 128 || K % 128 || K > 16384 ||
       logits_stride < N)
     return invalid("head arguments");
+  HeadArgs p{};
+  p.a_scale = a_scale; p.w_scale = w_scale; p.logits = logits; p.ldl = logits_stride;
+  p.M = M; p.N = N; p.K = K; p.error_flag = error_flag;
+  return run_head(a_e4m3, a_scale, w_e4m3, w_scale, p, stream);
+}
+
+extern "C" int ds41_b200_head_fp8_scatter(const void *a_e4m3, const float *a_scale, const void *w_e4m3,
+                                          const float *w_scale, float *const *owner_logits, int owners,
+                                          int rows_per_owner, int64_t logits_stride, int vocab_offset, int M, int N,
+                                          int K, int *error_flag, cudaStream_t stream) {
+  if (!a_e4m3 || !a_scale || !w_e4m3 || !w_scale || !owner_logits || M < 1 || N < 1 || K < 128 || K % 128 ||
+      K > 16384 || owners < 1 || owners > kMaxOwners || rows_per_owner < 1 || vocab_offset < 0 ||
+      logits_stride < int64_t(vocab_offset) + N || int64_t(owners) * rows_per_owner < M)
+    return invalid("scattered head arguments");
+  HeadArgs p{};
+  p.a_scale = a_scale; p.w_scale = w_scale; p.logits = nullptr; p.ldl = logits_stride;
+  p.M = M; p.N = N; p.K = K; p.error_flag = error_flag;
+  p.rows_per_owner = rows_per_owner; p.col_offset = vocab_offset;
+  for (int r = 0; r < owners; ++r) {
+    if (!owner_logits[r] && int64_t(r) * rows_per_owner < M) return invalid("scattered head: null owner buffer");
+    p.owner_base[r] = owner_logits[r];
+  }
+  return run_head(a_e4m3, a_scale, w_e4m3, w_scale, p, stream);
+}
+
+namespace {
+int run_head(const void *a_e4m3, const float *a_scale, const void *w_e4m3, const float *w_scale, HeadArgs p,
+             cudaStream_t stream) {
+  (void)a_scale; (void)w_scale;
+  const int M = p.M, N = p.N, K = p.K;
   if ((reinterpret_cast<uintptr_t>(a_e4m3) & 15u) || (reinterpret_cast<uintptr_t>(w_e4m3) & 15u))
     return invalid("head operands must be 16-byte aligned");
   int dev = 0, sms = 0;
@@ -392,7 +440,6 @@ extern "C" int ds41_b200_head_fp8(const void *a_e4m3, const float *a_scale, cons
   CUtensorMap mw, ma;
   if (!make_map(&mw, w_e4m3, uint64_t(N), uint64_t(K), kTileN) || !make_map(&ma, a_e4m3, uint64_t(M), uint64_t(K), uint32_t(cols)))
     return invalid("cuTensorMapEncodeTiled failed");
-  HeadArgs p{a_scale, w_scale, logits, logits_stride, M, N, K, error_flag};
   switch (cols) {
     case 16: e = launch_head<16, 1>(mw, ma, p, sms, stream); break;
     case 32: e = launch_head<32, 1>(mw, ma, p, sms, stream); break;
@@ -401,6 +448,7 @@ extern "C" int ds41_b200_head_fp8(const void *a_e4m3, const float *a_scale, cons
   }
   return int(e);
 }
+}  // namespace
 
 extern "C" size_t ds41_fuse_head_fp8_workspace_bytes(int M, int K) {
   if (M < 1 || K < 128 || K % 128) return 0;

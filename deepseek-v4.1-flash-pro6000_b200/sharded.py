@@ -1,10 +1,21 @@
-"""Vocabulary-sharded sampling across the GPUs of one node (one process per GPU, torch.distributed for the exchange).
+"""Vocabulary-sharded decode tail across the GPUs of one node (one process per GPU, torch.distributed for the plumbing).
 
 Rank r owns the contiguous id range produced by `shard_plan` (128-row blocks of the head's weight matrix, uneven by
-at most one block).  Per step: local candidates (CUDA) -> one all-gather of 544-byte records (one per 8192 ids) per row (NCCL on GPUs,
-gloo in the CPU tests) -> combine (CUDA, replicated on every rank).  Rows the combine cannot certify as covered are
-re-sampled from their full logits, gathered only for those rows.
+at most one block).  Two exchanges are implemented:
+
+* candidates (`ShardedSampler`): local candidates (CUDA) -> one all-gather of 544-byte records (one per 8192 ids) per
+  row (NCCL on GPUs, gloo in the CPU tests) -> combine (CUDA, replicated on every rank).  Rows the combine cannot
+  certify as covered are re-sampled from their full logits, gathered only for those rows.  Cheap when the nucleus is
+  small (trained models: a few dozen ids); useless when it is not.
+* rows (`RowExchange` + `ShardedDecodeTail`): the head kernel's epilogue stores each row's vocabulary slice straight
+  into the full-vocabulary buffer of the rank that owns the row (peer stores over NVLink, overlapped with the GEMM), a
+  one-word all-reduce orders readers after writers, every rank samples its rows with the single-GPU sampler, and one
+  small all-gather publishes tokens and status.  Cost is independent of the distribution; this is what flat
+  distributions (a randomly initialised head: nuclei of tens of thousands of ids) need.
+
+`ShardedDecodeTail` picks between them from the coverage it observes.
 """
+import math
 import ctypes as C
 
 import torch
@@ -125,3 +136,154 @@ class ShardedSampler:
 
     def sample_full(self, full, seeds, steps, slot, purpose):
         return self.pkg.sample_logits(full, self.t, self.top_p, seeds, steps, slot=slot, purpose=purpose)
+
+
+class _DeviceBlock:
+    """Minimal CUDA array interface over a raw device pointer, so that torch can view library-allocated memory."""
+
+    def __init__(self, ptr, shape, typestr):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False),
+                                         "version": 2, "strides": None}
+
+
+def rows_plan(rows, world):
+    """Rows per owner (ceil) and [(first row, count)] per rank: contiguous blocks, the tail ranks may hold fewer."""
+    per = max(1, math.ceil(rows / world))
+    return per, [(min(rows, r * per), max(0, min(rows, (r + 1) * per) - min(rows, r * per))) for r in range(world)]
+
+
+class RowExchange:
+    """One peer-visible full-vocabulary logits buffer [rows_per_owner, vocab] per rank, mapped into every rank."""
+
+    def __init__(self, pkg, device, rows, vocab, group=None):
+        self.pkg, self.device, self.rows, self.vocab, self.group = pkg, device, rows, vocab, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.rows_per_owner, plan = rows_plan(rows, self.world)
+        self.row0, self.my_rows = plan[self.rank]
+        lib = pkg.lib()
+        lib.ds41_b200_peer_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]
+        lib.ds41_b200_peer_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+        lib.ds41_b200_peer_close.argtypes = [C.c_void_p]
+        lib.ds41_b200_peer_free.argtypes = [C.c_void_p]
+        lib.ds41_b200_head_fp8_scatter.argtypes = [C.c_void_p] * 4 + [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int64,
+                                                                      C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                                                      C.c_void_p]
+        self._lib = lib
+        handle = C.create_string_buffer(64)
+        mine = C.c_void_p()
+        with torch.cuda.device(device):
+            rc = lib.ds41_b200_peer_alloc(self.rows_per_owner * vocab * 4, C.byref(mine), handle)
+        if rc:
+            raise RuntimeError(f"ds41_b200_peer_alloc: cudaError {rc} ({pkg.last_error()})")
+        self._mine = mine
+        handles = [None] * self.world
+        if self.world > 1:
+            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        else:
+            handles[0] = bytes(handle.raw)
+        self._opened = []
+        ptrs = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                ptrs.append(mine.value)
+                continue
+            p = C.c_void_p()
+            with torch.cuda.device(device):
+                rc = lib.ds41_b200_peer_open(C.create_string_buffer(h, 64), C.byref(p))
+            if rc:
+                raise RuntimeError(f"ds41_b200_peer_open(rank {r}): cudaError {rc} ({pkg.last_error()})")
+            self._opened.append(p)
+            ptrs.append(p.value)
+        self.owner_ptrs = (C.c_void_p * self.world)(*ptrs)
+        self.full = torch.as_tensor(_DeviceBlock(mine.value, (self.rows_per_owner, vocab), "<f4"), device=device)
+        self.full.zero_()
+        self.word = torch.zeros(1, dtype=torch.int32, device=device)
+        self.packed = torch.full((2, self.rows_per_owner), -1, dtype=torch.int32, device=device)
+        self.everyone = torch.empty((self.world, 2, self.rows_per_owner), dtype=torch.int32, device=device)
+        if self.world > 1:
+            dist.barrier(group=group)  # every buffer exists and is mapped before anyone writes
+
+    def head_scatter(self, a, a_scale, w, w_scale, vocab_offset, error_flag=None):
+        """This rank's vocabulary slice of every row's logits, stored into the rows' owners."""
+        M, K = a.shape
+        with torch.cuda.device(self.device):
+            rc = self._lib.ds41_b200_head_fp8_scatter(a.data_ptr(), a_scale.data_ptr(), w.data_ptr(), w_scale.data_ptr(),
+                                                      self.owner_ptrs, self.world, self.rows_per_owner, self.vocab,
+                                                      vocab_offset, M, w.shape[0], K,
+                                                      error_flag.data_ptr() if error_flag is not None else None,
+                                                      C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        if rc:
+            raise RuntimeError(f"ds41_b200_head_fp8_scatter: cudaError {rc} ({self.pkg.last_error()})")
+
+    def writers_done(self):
+        """Stream-ordered: returns (on the stream) once every rank's head kernel has finished its peer stores."""
+        if self.world > 1:
+            dist.all_reduce(self.word, group=self.group)
+
+    def sample_mine(self, temperature, top_p, seeds, steps, slot=0, purpose=0, **kw):
+        n = self.my_rows
+        if n:
+            sl = slice(self.row0, self.row0 + n)
+            self.pkg.sample_logits(self.full[:n], temperature, top_p, seeds[sl], steps[sl], slot=slot, purpose=purpose,
+                                   tokens=self.packed[0, :n], status=self.packed[1, :n], **kw)
+
+    def publish(self, tokens, status):
+        """All-gather of every owner's (tokens, status); also orders the next step's writers after this step's readers."""
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.everyone.view(-1), self.packed.view(-1), group=self.group)
+        else:
+            self.everyone[0] = self.packed
+        tokens.copy_(self.everyone[:, 0, :].reshape(-1)[: self.rows])
+        status.copy_(self.everyone[:, 1, :].reshape(-1)[: self.rows])
+
+    def close(self):
+        for p in self._opened:
+            self._lib.ds41_b200_peer_close(p)
+        self._opened = []
+        if self._mine is not None:
+            self.full = None
+            self._lib.ds41_b200_peer_free(self._mine)
+            self._mine = None
+
+
+class ShardedDecodeTail:
+    """quantised activations -> this rank's head slice -> tokens for all rows on every rank.
+
+    strategy "rows" / "candidates" fix the exchange; "auto" starts with candidates and switches to rows for
+    `probe_every` steps whenever more than a quarter of the rows of a step were not covered."""
+
+    def __init__(self, pkg, device, rows, vocab_offset, vocab_local, vocab, temperature, top_p, strategy="auto",
+                 group=None, probe_every=256):
+        self.pkg, self.device, self.rows, self.v0, self.vn, self.vocab = pkg, device, rows, vocab_offset, vocab_local, vocab
+        self.t, self.top_p, self.strategy, self.probe_every = temperature, top_p, strategy, probe_every
+        self.rows_mode_left = 0
+        self.exchange = RowExchange(pkg, device, rows, vocab, group) if strategy != "candidates" else None
+        self.cands = None
+        if strategy != "rows":
+            self.cands = ShardedSampler(pkg, torch, device, rows, vocab_offset, vocab_local, vocab, temperature, top_p, group)
+            self.local_logits = torch.empty((rows, vocab_local), dtype=torch.float32, device=device)
+        self.steps_rows = self.steps_candidates = 0
+
+    def mode(self):
+        if self.strategy != "auto":
+            return self.strategy
+        return "rows" if self.rows_mode_left > 0 else "candidates"
+
+    def step(self, a, a_scale, w, w_scale, seeds, steps, tokens, status, error_flag=None, slot=0, purpose=0):
+        if self.mode() == "rows":
+            ex = self.exchange
+            ex.head_scatter(a, a_scale, w, w_scale, self.v0, error_flag)
+            ex.writers_done()
+            ex.sample_mine(self.t, self.top_p, seeds, steps, slot, purpose, scratch=None)
+            ex.publish(tokens, status)
+            self.rows_mode_left -= 1
+            self.steps_rows += 1
+            return "rows"
+        self.pkg.head_fp8(a, a_scale, w, w_scale, self.local_logits, error_flag)
+        before = self.cands.escalated
+        self.cands.sample(self.local_logits, seeds, steps, tokens, status, slot, purpose)
+        self.steps_candidates += 1
+        if self.strategy == "auto" and (self.cands.escalated - before) * 4 > self.rows:
+            self.rows_mode_left = self.probe_every
+        return "candidates"

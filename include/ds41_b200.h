@@ -187,6 +187,27 @@ typedef struct ds41_b200_shard_combine_args {
 } ds41_b200_shard_combine_args;
 int ds41_b200_shard_combine(const ds41_b200_shard_combine_args *args, cudaStream_t stream);
 
+/* ---- vocabulary-sharded head with the row exchange fused into its epilogue ----------------------------------------
+ * No counterpart in the reference (single GPU).  The batch rows are split over `owners` ranks, rows_per_owner each
+ * (the last owner may hold fewer); owner_logits[r] is rank r's full-vocabulary buffer [rows_per_owner, logits_stride],
+ * mapped into this process (ds41_b200_peer_open) or local for r = this rank.  The kernel computes this rank's slice
+ * [vocab_offset, vocab_offset + N) of every row's logits and stores row m into owner m / rows_per_owner at local row
+ * m % rows_per_owner with plain peer stores, so the exchange (vocabulary-sharded -> row-sharded) overlaps the GEMM.
+ * The caller orders the owners' readers after every rank's kernel (a stream-ordered collective such as a one-word
+ * all-reduce) and the next step's writers after the readers (the token all-gather does that).
+ * owner_logits is a HOST array of `owners` device pointers, copied at the call. */
+int ds41_b200_head_fp8_scatter(const void *a_e4m3, const float *a_scale, const void *w_e4m3, const float *w_scale,
+                               float *const *owner_logits, int owners, int rows_per_owner, int64_t logits_stride,
+                               int vocab_offset, int M, int N, int K, int *error_flag, cudaStream_t stream);
+/* Peer-visible device buffers (CUDA IPC; one process per GPU).  alloc: cudaMalloc + a 64-byte handle to hand to the
+ * other ranks; open: map another rank's buffer (enables peer access to its device on first use); close / free undo
+ * them.  Not stream ordered: set up once, outside the decode loop. */
+#define DS41_B200_PEER_HANDLE_BYTES 64
+int ds41_b200_peer_alloc(size_t bytes, void **ptr, void *handle);
+int ds41_b200_peer_open(const void *handle, void **ptr);
+int ds41_b200_peer_close(void *ptr);
+int ds41_b200_peer_free(void *ptr);
+
 #ifdef __cplusplus
 }
 #endif

@@ -85,3 +85,58 @@ def test_head_argument_errors(pkg):
         pkg.head_fp8(a, torch.zeros(4, 1, device="cuda"), torch.zeros(128, 100, dtype=torch.uint8, device="cuda"),
                      torch.zeros(1, 1, device="cuda"))
     assert pkg.fuse_head_fp8_workspace_bytes(4, 100) == 0
+
+
+@pytest.mark.parametrize("M,owners", [(5, 2), (64, 4), (200, 8), (130, 3)])
+def test_head_scatter_to_row_owners(pkg, oracle, M, owners):
+    """Vocabulary-sharded head with the row exchange in its epilogue: every "rank" (all emulated on one GPU, one
+    launch each over its vocabulary slice) stores row m into owner m / rows_per_owner; the owners' buffers together
+    must equal the unsharded head bit for bit."""
+    import importlib
+    sharded = importlib.import_module("ds41_b200.sharded")
+    N, K = 1000, 512
+    x = oracle.gen_normal(5, M, (M, K), 1.0)
+    w = oracle.gen_normal(6, N, (N, K), 0.02)
+    xt = torch.from_numpy(oracle_lib.float_to_bf16_bits(x).view(np.int16)).cuda().view(torch.bfloat16)
+    a, a_scale = pkg.quantize_activations(xt)
+    wq, ws = oracle.quantize_weights(w)
+    wq, ws = torch.from_numpy(wq).cuda(), torch.from_numpy(ws).cuda()
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    want = pkg.head_fp8(a, a_scale, wq, ws, error_flag=flag)
+    per, plan = sharded.rows_plan(M, owners)
+    assert sum(n for _, n in plan) == M
+    bufs = [torch.full((per, N), float("nan"), device="cuda") for _ in range(owners)]
+    ex = sharded.RowExchange.__new__(sharded.RowExchange)  # buffers are local here: no IPC, only the launch wrapper
+    ex.pkg, ex.device, ex.world, ex.rows_per_owner, ex.vocab = pkg, torch.device("cuda", 0), owners, per, N
+    import ctypes as C
+    ex._lib = pkg.lib()
+    ex._lib.ds41_b200_head_fp8_scatter.argtypes = [C.c_void_p] * 4 + [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int64,
+                                                                     C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    ex.owner_ptrs = (C.c_void_p * owners)(*[b.data_ptr() for b in bufs])
+    for v0, vn in sharded.shard_plan(N, owners):
+        if vn:
+            ex.head_scatter(a, a_scale, wq[v0:v0 + vn], ws[v0 // 128:(v0 + vn + 127) // 128], v0, flag)
+    torch.cuda.synchronize()
+    assert flag.item() == 0
+    got = torch.cat([b[:n] for b, (_, n) in zip(bufs, plan)])
+    assert torch.equal(got, want)
+
+
+def test_peer_buffer_alloc_and_view(pkg):
+    """Library-allocated peer-visible buffer: allocation, 64-byte handle, torch view, free (mapping into another
+    process needs a second process and is exercised by the multi-GPU bench)."""
+    import ctypes as C
+    import importlib
+    sharded = importlib.import_module("ds41_b200.sharded")
+    lib = pkg.lib()
+    lib.ds41_b200_peer_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]
+    lib.ds41_b200_peer_free.argtypes = [C.c_void_p]
+    handle, ptr = C.create_string_buffer(64), C.c_void_p()
+    assert lib.ds41_b200_peer_alloc(4096 * 4, C.byref(ptr), handle) == 0 and ptr.value
+    assert any(handle.raw)
+    t = torch.as_tensor(sharded._DeviceBlock(ptr.value, (4, 1024), "<f4"), device="cuda")
+    t.fill_(3.0)
+    assert t.sum().item() == 3.0 * 4096
+    del t
+    assert lib.ds41_b200_peer_free(ptr) == 0
+    assert lib.ds41_b200_peer_alloc(0, C.byref(ptr), handle) != 0

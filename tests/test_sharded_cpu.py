@@ -133,3 +133,17 @@ def test_two_rank_exchange_and_escalation_on_gloo():
         assert len(out) == world
         for rank in range(world):
             assert out[rank] == [], out[rank]
+
+
+def test_rows_plan_covers_every_row_once():
+    sys.path.insert(0, ROOT)
+    import __graft_entry__ as entry
+    entry.load_package()
+    sharded = importlib.import_module("ds41_b200.sharded")
+    for rows in (1, 7, 64, 1000, 1024):
+        for world in (1, 2, 3, 4, 8):
+            per, plan = sharded.rows_plan(rows, world)
+            assert per * world >= rows and len(plan) == world
+            covered = [r for first, n in plan for r in range(first, first + n)]
+            assert covered == list(range(rows))
+            assert all(first == min(rows, r * per) for r, (first, _) in enumerate(plan))
