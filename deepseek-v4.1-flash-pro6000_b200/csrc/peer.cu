@@ -1,7 +1,7 @@
 // Peer-visible device buffers for the vocabulary-sharded path: one process per GPU, each exports one buffer (the full
 // logits rows it will sample) and maps the other ranks' buffers, so that the head kernel's epilogue can store its
-// vocabulary slice of every row directly into the row's owner (ds41_b200_head_fp8_scatter).  Plain CUDA IPC: no
-// multicast object is created and nothing here is bound to NVLink multicast.
+// vocabulary slice of every row directly into the row's owner (ds41_b200_head_fp8_scatter).  Plain CUDA IPC mappings,
+// written with ordinary peer stores: no NVSwitch group object is created for them.
 #include <cuda_runtime.h>
 
 #include <cstring>

@@ -18,6 +18,7 @@
 #include <stdint.h>
 
 namespace ds41 {
+
 namespace cg = cooperative_groups;
 
 constexpr int kThreads = 512;
@@ -80,6 +81,56 @@ struct Slot {  // one CTA's contribution to a cluster-wide exchange
   float f[2];
   int i[6];
 };
+
+// exp(x) for x <= 0, the only arguments the samplers have ((logit - row maximum) / T).  Table-driven:
+// x = (64 k + j) ln2/64 + r with |r| <= ln2/128, exp(x) = 2^k * 2^(j/64) * exp(r), exp(r) - 1 from a degree-6 Taylor
+// polynomial (truncation < 3e-20), the reduction with ln2/64 split into a 32-bit head and a tail so that n * head is
+// exact.  Error: half an ulp from the table entry, half an ulp from the final fused multiply-add, < 0.01 ulp from the
+// rest: below 1.01 ulp, i.e. a relative error < 2.1 * 2^-53, which the decision bounds of every caller allow for
+// (they budget tens of units per weight).  Results below the normal range (x < -708) are returned as 0: such a weight
+// is < 1e-307 of the row's largest, which no comparison made on the sums can see.  12 FP64 instructions against the
+// library routine's ~47.
+static __device__ const double kExp2Table[64] = {
+    0x1.0000000000000p+0, 0x1.02c9a3e778061p+0, 0x1.059b0d3158574p+0, 0x1.0874518759bc8p+0,
+    0x1.0b5586cf9890fp+0, 0x1.0e3ec32d3d1a2p+0, 0x1.11301d0125b51p+0, 0x1.1429aaea92de0p+0,
+    0x1.172b83c7d517bp+0, 0x1.1a35beb6fcb75p+0, 0x1.1d4873168b9aap+0, 0x1.2063b88628cd6p+0,
+    0x1.2387a6e756238p+0, 0x1.26b4565e27cddp+0, 0x1.29e9df51fdee1p+0, 0x1.2d285a6e4030bp+0,
+    0x1.306fe0a31b715p+0, 0x1.33c08b26416ffp+0, 0x1.371a7373aa9cbp+0, 0x1.3a7db34e59ff7p+0,
+    0x1.3dea64c123422p+0, 0x1.4160a21f72e2ap+0, 0x1.44e086061892dp+0, 0x1.486a2b5c13cd0p+0,
+    0x1.4bfdad5362a27p+0, 0x1.4f9b2769d2ca7p+0, 0x1.5342b569d4f82p+0, 0x1.56f4736b527dap+0,
+    0x1.5ab07dd485429p+0, 0x1.5e76f15ad2148p+0, 0x1.6247eb03a5585p+0, 0x1.6623882552225p+0,
+    0x1.6a09e667f3bcdp+0, 0x1.6dfb23c651a2fp+0, 0x1.71f75e8ec5f74p+0, 0x1.75feb564267c9p+0,
+    0x1.7a11473eb0187p+0, 0x1.7e2f336cf4e62p+0, 0x1.82589994cce13p+0, 0x1.868d99b4492edp+0,
+    0x1.8ace5422aa0dbp+0, 0x1.8f1ae99157736p+0, 0x1.93737b0cdc5e5p+0, 0x1.97d829fde4e50p+0,
+    0x1.9c49182a3f090p+0, 0x1.a0c667b5de565p+0, 0x1.a5503b23e255dp+0, 0x1.a9e6b5579fdbfp+0,
+    0x1.ae89f995ad3adp+0, 0x1.b33a2b84f15fbp+0, 0x1.b7f76f2fb5e47p+0, 0x1.bcc1e904bc1d2p+0,
+    0x1.c199bdd85529cp+0, 0x1.c67f12e57d14bp+0, 0x1.cb720dcef9069p+0, 0x1.d072d4a07897cp+0,
+    0x1.d5818dcfba487p+0, 0x1.da9e603db3285p+0, 0x1.dfc97337b9b5fp+0, 0x1.e502ee78b3ff6p+0,
+    0x1.ea4afa2a490dap+0, 0x1.efa1bee615a27p+0, 0x1.f50765b6e4540p+0, 0x1.fa7c1819e90d8p+0};
+
+__device__ __forceinline__ double exp_nonpos(double x) {
+  constexpr double kInvL = 0x1.71547652b82fep+6;    // 64 / ln 2
+  constexpr double kLHead = 0x1.62e42fee00000p-7;   // ln 2 / 64, upper 32 bits
+  constexpr double kLTail = 0x1.a39ef35793c76p-39;  // and the rest
+  constexpr double kMagic = 6755399441055744.0;     // 1.5 * 2^52: adding it leaves round(x * kInvL) in the low word
+  const bool tiny = !(x >= -708.0);  // also NaN, which the callers have excluded (non-finite rows are rejected)
+  x = tiny ? -708.0 : x;               // branch free: independent calls can overlap
+  const double t = fma(x, kInvL, kMagic);
+  const int n = __double2loint(t);
+  const double nd = t - kMagic;
+  double r = fma(nd, -kLHead, x);
+  r = fma(nd, -kLTail, r);
+  double q = fma(r, 1.0 / 720.0, 1.0 / 120.0);
+  q = fma(q, r, 1.0 / 24.0);
+  q = fma(q, r, 1.0 / 6.0);
+  q = fma(q, r, 0.5);
+  q = fma(q, r, 1.0);
+  q *= r;  // exp(r) - 1
+  const double table = __ldg(&kExp2Table[n & 63]);
+  const double v = fma(table, q, table);
+  const double scaled = __hiloint2double(__double2hiint(v) + (n >> 6) * 1048576, __double2loint(v));
+  return tiny ? 0.0 : scaled;
+}
 
 struct __align__(128) RowSmem {
   float y[kSliceCap];  // staged logits, rewritten in place as effective logits (-inf = excluded)

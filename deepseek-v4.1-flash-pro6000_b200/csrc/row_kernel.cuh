@@ -68,39 +68,77 @@ __device__ int draw_token(RowCtx &c, double u, double rel_bound, double abs_boun
   *total_out = total;
   const double target = u * total;
   const double slack = rel_bound * total + abs_bound;
-  double inner = 0;
-  for (int w = 0; w < c.warp; ++w) inner += s->warp_sum[w];
-  const double start = prefix + inner, end = prefix + (inner + s->warp_sum[c.warp]);
-  int found = -1, amb = 0;
-  if (start <= target && target < end) {  // exactly one warp of the cluster owns the target (intervals tile [0,total))
-    double carry = start;
-    int last_positive = -1;
-    for (int it = 0; it < c.region && found < 0; it += 32) {
-      const int j = c.warp * c.region + it + c.lane;
-      const double v = j < c.len ? value(j) : 0.0;
-      double scan = v;
+  // Which warp region of this CTA holds the target, if any (the regions' intervals tile [0, total), so exactly one
+  // region of the cluster does); every thread evaluates the same sums, so the answer is uniform in the CTA.
+  int owner_warp = -1, amb = 0;
+  double region_start = 0;
+  {
+    double inner = 0;
+    for (int w = 0; w < kWarps; ++w) {
+      const double start = prefix + inner, end = prefix + (inner + s->warp_sum[w]);
+      if (owner_warp < 0 && start <= target && target < end) { owner_warp = w; region_start = start; }
+      inner += s->warp_sum[w];
+    }
+  }
+  if (owner_warp >= 0) {
+    // The whole CTA walks the owning region: warp v takes chunk v of it (one or two 32-id blocks, values kept in
+    // registers), the chunk sums locate the chunk that holds the target, and that chunk's warp walks its values.
+    const int blocks = (c.region / kWarps + 31) / 32;  // 32-id blocks per chunk: 1 or 2 (region <= 1024)
+    const int first = owner_warp * c.region + c.warp * blocks * 32;
+    double v[2] = {0.0, 0.0};
+    int last_mine = -1;
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const double t = __shfl_up_sync(0xffffffffu, scan, o);
-        if (c.lane >= o) scan += t;
-      }
-      const double cum = carry + scan;
-      const unsigned hit = __ballot_sync(0xffffffffu, v > 0 && target < cum);
-      const unsigned pos = __ballot_sync(0xffffffffu, v > 0);
-      if (hit) {
-        const int l = __ffs(hit) - 1;
-        found = c.begin + c.warp * c.region + it + l;
-        const double cum_l = __shfl_sync(0xffffffffu, cum, l);
-        const double v_l = __shfl_sync(0xffffffffu, v, l);
-        const double below = cum_l - v_l;  // CDF before the chosen id
-        amb = (cum_l - target < slack) || (below > 0 && target - below < slack);
-      } else {
-        if (pos) last_positive = c.begin + c.warp * c.region + it + (31 - __clz(pos));
-        carry = __shfl_sync(0xffffffffu, cum, 31);
+    for (int b = 0; b < 2; ++b) {
+      const int idx = c.warp * blocks * 32 + b * 32 + c.lane, j = first + b * 32 + c.lane;
+      const bool in = b < blocks && idx < c.region && j < c.len;
+      const double w = value(in ? j : 0);
+      v[b] = in ? w : 0.0;
+      if (v[b] > 0) last_mine = j;
+    }
+    double chunk = v[0] + v[1];
+#pragma unroll
+    for (int o = 16; o; o >>= 1) chunk += __shfl_xor_sync(0xffffffffu, chunk, o);
+    last_mine = __reduce_max_sync(0xffffffffu, last_mine);
+    if (c.lane == 0) { s->red_d[c.warp] = chunk; s->red_i[c.warp] = last_mine; }
+    __syncthreads();
+    int owner_chunk = -1, last_positive = -1;
+    double carry = region_start;
+    {
+      double run = region_start;
+      for (int w = 0; w < kWarps; ++w) {
+        const double through = run + s->red_d[w];
+        if (owner_chunk < 0 && s->red_d[w] > 0 && target < through) { owner_chunk = w; carry = run; }
+        run = through;
+        last_positive = max(last_positive, s->red_i[w]);
       }
     }
-    if (found < 0) { found = last_positive; amb = 1; }  // rounding left the target past this region's last step
-    if (c.lane == 0) { s->bcast_i[0] = found; s->bcast_i[1] = amb; s->bcast_i[2] = 1; }
+    if (last_positive >= 0) last_positive += c.begin;
+    int found = -1;
+    if (c.warp == (owner_chunk < 0 ? 0 : owner_chunk)) {
+      for (int b = 0; b < blocks && found < 0 && owner_chunk >= 0; ++b) {
+        const double vb = b ? v[1] : v[0];
+        double sc = vb;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const double up = __shfl_up_sync(0xffffffffu, sc, o);
+          if (c.lane >= o) sc += up;
+        }
+        const double cum = carry + sc;
+        const unsigned hit = __ballot_sync(0xffffffffu, vb > 0 && target < cum);
+        if (hit) {
+          const int h = __ffs(hit) - 1;
+          found = c.begin + first + b * 32 + h;
+          const double cum_h = __shfl_sync(0xffffffffu, cum, h);
+          const double v_h = __shfl_sync(0xffffffffu, vb, h);
+          const double below = cum_h - v_h;  // CDF before the chosen id
+          amb = (cum_h - target < slack) || (below > 0 && target - below < slack);
+        } else {
+          carry = __shfl_sync(0xffffffffu, cum, 31);
+        }
+      }
+      if (found < 0) { found = last_positive; amb = 1; }  // rounding left the target past the region's last step
+      if (c.lane == 0) { s->bcast_i[0] = found; s->bcast_i[1] = amb; s->bcast_i[2] = 1; }
+    }
   }
   __syncthreads();
   Slot res{};
@@ -201,15 +239,36 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
   __syncthreads();
   {
     Slot mine{};
-    block_argmax(c, best, best_id);
-    {  // block minimum through the order-preserving integer image of -lowest
-      const int bits = __float_as_int(-lowest);
-      const int top = block_max(c, bits >= 0 ? bits : bits ^ 0x7fffffff);
-      lowest = -__int_as_float(top >= 0 ? top : top ^ 0x7fffffff);
+    // one fused block reduction: (best, best_id) by "larger value, then lower id", lowest, flags, allowed
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_id, o);
+      if (ov > best || (ov == best && oi < best_id)) { best = ov; best_id = oi; }
+      lowest = fminf(lowest, __shfl_xor_sync(0xffffffffu, lowest, o));
     }
+    flags = int(__reduce_or_sync(0xffffffffu, unsigned(flags)));
+    allowed = __reduce_add_sync(0xffffffffu, allowed);
+    if (c.lane == 0) {
+      s->red_f[c.warp] = best; s->red_j[c.warp] = best_id; s->red_d[c.warp] = double(lowest);
+      s->red_q[c.warp] = (unsigned long long)(unsigned(allowed)) << 32 | unsigned(flags);
+    }
+    __syncthreads();
+    best = s->red_f[0]; best_id = s->red_j[0]; lowest = float(s->red_d[0]);
+    flags = int(unsigned(s->red_q[0])); allowed = int(s->red_q[0] >> 32);
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) {
+      const float ov = s->red_f[w];
+      const int oi = s->red_j[w];
+      if (ov > best || (ov == best && oi < best_id)) { best = ov; best_id = oi; }
+      lowest = fminf(lowest, float(s->red_d[w]));
+      flags |= int(unsigned(s->red_q[w]));
+      allowed += int(s->red_q[w] >> 32);
+    }
+    __syncthreads();
     mine.f[0] = best; mine.i[0] = best_id; mine.f[1] = lowest;
-    mine.i[1] = block_or(c, flags);
-    mine.i[2] = block_sum(c, allowed);
+    mine.i[1] = flags;
+    mine.i[2] = allowed;
     const Slot *all = exchange(c, mine);
     best = all[0].f[0]; best_id = all[0].i[0]; flags = all[0].i[1]; allowed = all[0].i[2];
     for (int r = 1; r < c.nranks; ++r) {
@@ -231,12 +290,13 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
   // exp((y - max)/T) with the division replaced by a multiplication: the argument moves by at most one ulp, the
   // value by |argument| * 2^-53 relative (< 100 u), which every comparison made on sums of these weights allows for
   const double inv_t = t > 0 ? 1.0 / t : 0.0;
-  auto weight = [max_logit, inv_t](float y) { return exp((double(y) - double(max_logit)) * inv_t); };
+  auto weight = [max_logit, inv_t](float y) { return exp_nonpos((double(y) - double(max_logit)) * inv_t); };
   Cut cut{-CUDART_INF_F, -1};
   // value of local id j for the sums and the draw: exp weight of a survivor of the CURRENT cut, else 0
   auto value = [&cut, &c, s, weight](int j) {
     const float y = s->y[j];
-    return survives(y, c.begin + j, cut) ? weight(y) : 0.0;
+    const double w = weight(y);  // unconditional (0 for an excluded id): independent calls overlap
+    return survives(y, c.begin + j, cut) ? w : 0.0;
   };
   int entered = allowed, kept = allowed;
   double z = 0, e_kept = 0;

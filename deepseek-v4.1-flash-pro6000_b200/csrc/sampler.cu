@@ -106,3 +106,17 @@ extern "C" int ds41_b200_sample_logits(const ds41_b200_sample_args *p, cudaStrea
   a.only_uncovered = 1;
   return int(launch_rows<kModeSample>(a, p->rows, stream));
 }
+
+namespace ds41 {
+__global__ void exp_probe_kernel(const double *x, double *out, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = exp_nonpos(x[i]);
+}
+}  // namespace ds41
+
+extern "C" int ds41_b200_test_exp_nonpos(const double *x, double *out, int n, cudaStream_t stream) {
+  if (!x || !out || n < 1) return invalid("exp probe arguments");
+  ds41::exp_probe_kernel<<<(n + 255) / 256, 256, 0, stream>>>(x, out, n);
+  return int(cudaGetLastError());
+}
+

@@ -41,7 +41,7 @@ struct Measure {  // one row's probability measure: P(id) = survives ? exp((x-ma
   double inv_t, inv_kept;  // 1/T and 1/e_kept: multiplications instead of divisions (a few ulp, inside bound())
   __device__ __forceinline__ double at(int id) const {
     const float y = __ldg(x + id);
-    return survives(y, id, st.cut) ? exp((double(y) - double(st.max_logit)) * inv_t) * inv_kept : 0.0;
+    return survives(y, id, st.cut) ? exp_nonpos((double(y) - double(st.max_logit)) * inv_t) * inv_kept : 0.0;
   }
   __device__ __forceinline__ double bound() const { return 2.0 * (double(st.kept) + 256.0) * kU; }
 };

@@ -208,6 +208,11 @@ int ds41_b200_peer_open(const void *handle, void **ptr);
 int ds41_b200_peer_close(void *ptr);
 int ds41_b200_peer_free(void *ptr);
 
+/* ---- test hook ---------------------------------------------------------------------------------------------------
+ * out[i] = the samplers' own exp(x[i]) for x <= 0 (device pointers), so that its error can be measured against a
+ * reference exponential.  No counterpart in the reference. */
+int ds41_b200_test_exp_nonpos(const double *x, double *out, int n, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

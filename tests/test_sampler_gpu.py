@@ -151,3 +151,29 @@ def test_losslessness_statistics(pkg):
     for j in range(4):
         expected = n * pe[j]
         assert abs((tok == j).sum() - expected) < 6 * np.sqrt(expected * (1 - pe[j])) + 2
+
+
+def test_exp_nonpos_within_one_ulp_of_reference(pkg):
+    """The samplers' table-driven exp for x <= 0 against numpy's long-double exp (64-bit mantissa): at most 1.01 ulp on
+    10 million arguments spread over the whole range, exact 1 at 0, zero below the normal range."""
+    import ctypes as C
+    lib = pkg.lib()
+    lib.ds41_b200_test_exp_nonpos.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+    rng = np.random.default_rng(5)
+    x = np.concatenate([-rng.random(4_000_000) * 40.0, -rng.random(4_000_000) * 708.0,
+                        -np.exp(rng.random(2_000_000) * 60.0 - 50.0).clip(max=708.0),
+                        np.array([0.0, -0.0, -708.0, -1e-300, -0.005415212348514943, -0.0054152123485])])
+    xt = torch.from_numpy(x).cuda()
+    out = torch.empty_like(xt)
+    assert lib.ds41_b200_test_exp_nonpos(xt.data_ptr(), out.data_ptr(), x.size, None) == 0
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    want = np.exp(x.astype(np.longdouble))
+    ulp = np.spacing(want.astype(np.float64)).astype(np.longdouble)
+    err = np.abs(got.astype(np.longdouble) - want) / ulp
+    assert err.max() <= 1.01, (err.max(), x[err.argmax()])
+    assert got[x == 0].tolist() == [1.0, 1.0]
+    below = torch.tensor([-708.5, -745.0, -1e9, float("-inf")], dtype=torch.float64, device="cuda")
+    o2 = torch.empty_like(below)
+    assert lib.ds41_b200_test_exp_nonpos(below.data_ptr(), o2.data_ptr(), 4, None) == 0
+    assert o2.cpu().tolist() == [0.0, 0.0, 0.0, 0.0]
