@@ -7,13 +7,15 @@
 // group) by the reference's power-of-two rule (dense.cu:8-16) widened to the weight block.  It keeps the plugin
 // conventions of fuse_head.h:8 (caller-owned buffers, stream-ordered, no allocation, no synchronisation).
 //
-// Kernel shape ("swap-AB" decode GEMM): the 128 vocabulary rows of a weight tile are the M dimension of
-// tcgen05.mma (one TMEM lane per vocabulary row) and the batch is its N dimension (16..128 TMEM columns), so a batch
-// of 1 wastes no tensor-core rows and the fp32 accumulators of one vocabulary row live in one thread of the
-// epilogue.  Per CTA: warp 0 streams W and A tiles with TMA (128-byte swizzle) into a ring of shared-memory stages,
-// warp 1 issues four K=32 tcgen05.mma per 128-wide K block into one of four TMEM accumulators, the epilogue warps
-// (one or two groups of four) pull each finished K block out of TMEM (tcgen05.ld), apply the combined scale in fp32
-// and keep the running sums in registers.
+// Kernel shape: an output tile is kRows batch rows x 128 vocabulary ids.  The batch rows are the M dimension of
+// tcgen05.mma (one TMEM lane per batch row; M is always 128, the activation tile holds kRows = 16..128 real rows and
+// the lanes beyond them are never read), the 128 vocabulary rows of a weight tile are its N dimension (128 TMEM
+// columns).  With this orientation the combined scale a_scale[m,kb] * w_scale[n/128,kb] of a K block is ONE number
+// per epilogue thread (its batch row; the weight block is the whole tile), so the fp32 promotion of a K block is a
+// register-only loop of fused multiply-adds.  Per CTA: warp 0 streams W and A tiles with TMA (128-byte swizzle) into
+// a ring of shared-memory stages, warp 1 issues four K=32 tcgen05.mma per 128-wide K block into one of four TMEM
+// accumulators, sixteen epilogue warps (lane quadrant x 32-column group) pull each finished K block out of TMEM
+// (tcgen05.ld), hand the accumulator back at once, scale and add in fp32 registers.
 // Every wait is bounded; on expiry the kernel raises *error_flag, frees its TMEM and returns.
 #include "ds41_b200.h"
 #include "host_error.h"
@@ -22,11 +24,12 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace ds41 {
 namespace {
 
-constexpr int kTileN = 128;   // vocabulary rows per tile (UMMA M)
+constexpr int kTileN = 128;   // vocabulary rows per tile (UMMA N; the UMMA M dimension, 128, takes the batch rows)
 constexpr int kTileK = 128;   // K elements per block = one 128-byte swizzle row of e4m3
 constexpr int kAccBufs = 4;   // TMEM accumulators in flight (K blocks between the MMA issuer and the epilogue)
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -47,51 +50,58 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
-// Bounded wait on a phase parity.  Returns false (and raises the abort flag) if the phase never completed.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, const Abort &ab) {
-  if (ab.set()) return false;
+// Bounded wait on a phase parity.  Returns false (and raises the abort flag) if the phase never completed.  The first
+// probe carries no other work: the single threads that issue the copies and the MMAs call this once or twice per K
+// block, and every instruction on their path delays the tensor pipe.
+__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(done)
+      : "r"(smem_addr(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+__device__ __noinline__ bool mbar_wait_slow(uint64_t *bar, uint32_t parity, volatile int *flag) {
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(done)
-        : "r"(smem_addr(bar)), "r"(parity)
-        : "memory");
-    if (done) return true;
-    if ((spin & 1023u) == 1023u && ab.set()) return false;
+    if (mbar_try(bar, parity)) return true;
+    if ((spin & 255u) == 255u && *flag != 0) return false;
   }
-  *ab.flag = 1;
+  *flag = 1;
   return false;
 }
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, const Abort &ab) {
+  if (mbar_try(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, ab.flag);
+}
 
-__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int y) {
+// Box {128 bytes, rows, K blocks} of the operand seen as [K/128][rows][128 bytes] (see make_map).
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int row, int kb) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::
           "r"(smem_addr(dst)),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(x), "r"(y)
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(x), "r"(row), "r"(kb)
       : "memory");
 }
 
 // Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows are 128 bytes apart, groups of 8 rows 1024 bytes
 // apart (stride byte offset), leading byte offset unused (1), descriptor version 1 for sm_100.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= uint64_t((saddr & 0x3FFFFu) >> 4);        // start address, bits [0,14)
-  d |= uint64_t(1) << 16;                        // leading byte offset (>>4), bits [16,30)
-  d |= uint64_t(1024 >> 4) << 32;                // stride byte offset (>>4), bits [32,46)
-  d |= uint64_t(1) << 46;                        // version, bits [46,48)
-  d |= uint64_t(2) << 61;                        // layout type SWIZZLE_128B, bits [61,64)
-  return d;
-}
-// Instruction descriptor for kind::f8f6f4, E4M3 x E4M3 -> F32, both operands K-major, M=128, N=columns.
+constexpr uint64_t kDescFixed = (uint64_t(1) << 16)              // leading byte offset (>>4), bits [16,30)
+                                | (uint64_t(1024 >> 4) << 32)    // stride byte offset (>>4), bits [32,46)
+                                | (uint64_t(1) << 46)            // version, bits [46,48)
+                                | (uint64_t(2) << 61);           // layout type SWIZZLE_128B, bits [61,64)
+// addr16 = shared-memory byte address >> 4 (start address field, bits [0,14); shared memory ends below 2^18 bytes)
+__device__ __forceinline__ uint64_t umma_desc16(uint32_t addr16) { return kDescFixed | uint64_t(addr16); }
+// Instruction descriptor for kind::f8f6f4, E4M3 x E4M3 -> F32, both operands K-major, M=128, N=n_cols.
 __host__ __device__ constexpr uint32_t umma_idesc(int n_cols) {
   return (1u << 4) | (uint32_t(n_cols >> 3) << 17) | (uint32_t(kTileN >> 4) << 24);
 }
-__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+template <bool kAccumulate>
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
   asm volatile(
       "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
       " tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "n"(kAccumulate ? 1 : 0)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
@@ -117,13 +127,27 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
 }
 
-template <int kCols>
+template <int kRows>
 struct HeadSmem {
-  static constexpr int kStageBytes = kTileN * kTileK + kCols * kTileK;
-  static constexpr int kStages = (200 * 1024 - 32 * kCols * 4) / kStageBytes > 12 ? 12 : (200 * 1024 - 32 * kCols * 4) / kStageBytes;
+  static constexpr int kStageBytes = kTileN * kTileK + kRows * kTileK;
+  // the MMA reads 128 activation rows from every stage; with kRows < 128 the rows beyond the tile belong to the next
+  // stage (or to the pad after the last one) and only feed TMEM lanes nobody reads
+  static constexpr int kPadBytes = (128 - kRows) * kTileK;
+  static constexpr int kMaxStages = 12;
+  // bytes beside the stages: alignment slack, pad, scale table [K/128][kRows], barriers and flags
+  static constexpr size_t fixed_bytes(int kblocks) {
+    return 1024 + kPadBytes + size_t(kblocks) * kRows * 4 + (2 * kMaxStages + 2 * kAccBufs) * 8 + 16;
+  }
+  // a stage holds `group` consecutive K blocks (one TMA box per operand)
+  static constexpr int stages(int kblocks, int group) {
+    const long long room = 226 * 1024 - (long long)fixed_bytes(kblocks);
+    const int n = room < 0 ? 0 : int(room / (kStageBytes * group));
+    return n > kMaxStages ? kMaxStages : n;
+  }
 };
 
 constexpr int kMaxOwners = 8;
+constexpr int kEpiWarps = 16, kHeadThreads = 64 + 32 * kEpiWarps;
 struct HeadArgs {
   const float *a_scale;  // [M, K/128]
   const float *w_scale;  // [ceil(N/128), K/128]
@@ -136,35 +160,40 @@ struct HeadArgs {
   // writes them with plain stores, so the vocabulary-to-row transposition rides on the GEMM.  rows_per_owner == 0: off.
   float *owner_base[kMaxOwners];
   int rows_per_owner, col_offset;
+  int stages;            // shared-memory stages of the TMA ring (host: HeadSmem::stages)
+  int group;             // K blocks per stage: every row of a weight tile is fetched as group*128 contiguous bytes
 };
 
-// kGroups epilogue warpgroups of 4 warps split the batch columns between them.
-template <int kCols, int kGroups>
-__global__ void __launch_bounds__(64 + 128 * kGroups, 1)
+template <int kRows>
+__global__ void __launch_bounds__(kHeadThreads, 1)
 head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, HeadArgs p) {
-  constexpr int kStages = HeadSmem<kCols>::kStages;
-  constexpr int kStageBytes = HeadSmem<kCols>::kStageBytes;
-  constexpr uint32_t kTmemCols = kAccBufs * kCols < 32 ? 32 : kAccBufs * kCols;
-  constexpr int kEpiThreads = 128 * kGroups, kMyCols = kCols / kGroups;
+  constexpr int kStageBytes = HeadSmem<kRows>::kStageBytes;
+  constexpr int kMaxStages = HeadSmem<kRows>::kMaxStages;
+  const int kStages = p.stages, group = p.group;
+  const int stage_bytes = kStageBytes * group, w_bytes = kTileN * kTileK * group;  // [W g0..][A g0..]
+  constexpr uint32_t kTmemCols = kAccBufs * kTileN;  // 512: four accumulators of 128 columns
+  constexpr int kQuads = (kRows + 31) / 32;          // lane quadrants that hold real batch rows
+  constexpr int kGroups = 4, kMyCols = kTileN / kGroups;  // 32-column groups: warp (quadrant q, group g)
+  constexpr int kEpiActive = 32 * kQuads * kGroups;  // epilogue threads that take part
   extern __shared__ __align__(1024) unsigned char smem[];
-  // carve: [stages][W tile 16 KB | A tile kCols*128 B], then the activation-scale table, then barriers
+  // carve: [stages][W tile 16 KB | A tile kRows*128 B], pad, then the activation-scale table, then barriers
   unsigned char *tiles = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~uintptr_t(1023));
-  float *sx = reinterpret_cast<float *>(tiles + size_t(kStages) * kStageBytes);  // [K/128][kCols]
+  float *sa = reinterpret_cast<float *>(tiles + size_t(kStages) * stage_bytes + HeadSmem<kRows>::kPadBytes);  // [K/128][kRows]
   const int kblocks = p.K / kTileK;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(sx + size_t(kblocks) * kCols);
-  uint64_t *full = bars, *empty = bars + kStages, *acc_full = bars + 2 * kStages, *acc_empty = acc_full + kAccBufs;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(sa + size_t(kblocks) * kRows);
+  uint64_t *full = bars, *empty = bars + kMaxStages, *acc_full = bars + 2 * kMaxStages, *acc_empty = acc_full + kAccBufs;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + kAccBufs);
   int *abort_word = reinterpret_cast<int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_tiles = (p.N + kTileN - 1) / kTileN, b_tiles = (p.M + kCols - 1) / kCols;
-  const int total_tiles = n_tiles * b_tiles;
+  const int n_tiles = (p.N + kTileN - 1) / kTileN, b_tiles = (p.M + kRows - 1) / kRows;
+  const int total_tiles = n_tiles * b_tiles;  // tile t = (vocabulary tile t / b_tiles, batch tile t % b_tiles)
   Abort ab{abort_word};
 
   if (threadIdx.x == 0) {
     *abort_word = 0;
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < kAccBufs; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4 * kGroups); }
+    for (int b = 0; b < kAccBufs; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], kQuads * kGroups); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {  // TMEM allocation by one full warp; the address lands in shared memory
@@ -182,12 +211,12 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       uint32_t stage = 0, phase = 0;
       for (int tile = blockIdx.x; tile < total_tiles && !ab.set(); tile += gridDim.x) {
         const int nt = tile / b_tiles, bt = tile % b_tiles;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb = 0; kb < kblocks; kb += group) {
           if (!mbar_wait(&empty[stage], phase ^ 1, ab)) break;
-          unsigned char *w_dst = tiles + size_t(stage) * kStageBytes, *a_dst = w_dst + kTileN * kTileK;
-          mbar_expect_tx(&full[stage], uint32_t(kStageBytes));
-          tma_load_2d(w_dst, &map_w, &full[stage], kb * kTileK, nt * kTileN);
-          tma_load_2d(a_dst, &map_a, &full[stage], kb * kTileK, bt * kCols);
+          unsigned char *w_dst = tiles + size_t(stage) * stage_bytes, *a_dst = w_dst + w_bytes;
+          mbar_expect_tx(&full[stage], uint32_t(stage_bytes));
+          tma_load_3d(w_dst, &map_w, &full[stage], 0, nt * kTileN, kb);
+          tma_load_3d(a_dst, &map_a, &full[stage], 0, bt * kRows, kb);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -195,101 +224,94 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (one lane)
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(kCols);
+      constexpr uint32_t idesc = umma_idesc(kTileN);
+      const uint32_t tiles16 = smem_addr(tiles) >> 4, stage16 = uint32_t(stage_bytes) >> 4;
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       for (int tile = blockIdx.x; tile < total_tiles && !ab.set(); tile += gridDim.x) {
-        for (int kb = 0; kb < kblocks; ++kb) {
-          if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, ab)) break;
+        bool ok = true;
+        for (int kb = 0; kb < kblocks && ok; kb += group) {
           if (!mbar_wait(&full[stage], phase, ab)) break;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t w_addr = smem_addr(tiles + size_t(stage) * kStageBytes), a_addr = w_addr + kTileN * kTileK;
-          const uint32_t d_addr = tmem_base + acc * kCols;
-#pragma unroll
-          for (int k = 0; k < kTileK / 32; ++k)
-            umma_f8(d_addr, umma_desc(w_addr + k * 32), umma_desc(a_addr + k * 32), idesc, k ? 1u : 0u);
-          umma_commit(&empty[stage]);    // stage may be refilled once these MMAs have read it
-          umma_commit(&acc_full[acc]);   // accumulator of this K block is complete
+          uint32_t w16 = tiles16 + stage * stage16, a16 = w16 + (w_bytes >> 4);  // addresses >> 4
+          for (int g = 0; g < group; ++g) {
+            if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, ab)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t d_addr = tmem_base + acc * kTileN;
+            // D[batch row, vocabulary id] (+)= A[batch row, k] * W[vocabulary id, k], K = 32 bytes per instruction
+            umma_f8<false>(d_addr, umma_desc16(a16), umma_desc16(w16), idesc);
+            umma_f8<true>(d_addr, umma_desc16(a16 + 2), umma_desc16(w16 + 2), idesc);
+            umma_f8<true>(d_addr, umma_desc16(a16 + 4), umma_desc16(w16 + 4), idesc);
+            umma_f8<true>(d_addr, umma_desc16(a16 + 6), umma_desc16(w16 + 6), idesc);
+            umma_commit(&acc_full[acc]);   // accumulator of this K block is complete
+            if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1; }
+            w16 += (kTileN * kTileK) >> 4; a16 += (kRows * kTileK) >> 4;
+          }
+          if (ok) umma_commit(&empty[stage]);  // the stage may be refilled once these MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1; }
-          if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1; }
         }
       }
     }
-  } else {
-    // ------------------------------------------------------------------ epilogue: 4 warps per group, one TMEM lane
-    // quadrant each; group g owns the batch columns [g*kMyCols, (g+1)*kMyCols)
-    const int quad = warp & 3;                      // TMEM lanes [32*quad, 32*quad+32) are readable by this warp
-    const int et = threadIdx.x - 64;                // 0..kEpiThreads-1
-    const int group = et >> 7, col0 = group * kMyCols;
+  } else if ((warp & 3) < kQuads) {
+    // ------------------------------------------------------------------ epilogue: warp = (lane quadrant, column group)
+    const int quad = warp & 3;          // TMEM lanes [32*quad, 32*quad+32) are readable by this warp: batch rows
+    const int group = (warp - 2) >> 2;  // vocabulary ids [32*group, 32*group+32) of the tile
+    const int row = quad * 32 + lane;   // batch row inside the tile
+    const int et = (group * kQuads + quad) * 32 + lane;  // 0..kEpiActive-1
+    const uint32_t lane_base = tmem_base + group * kMyCols + (uint32_t(quad * 32) << 16);
     uint32_t acc = 0, acc_phase = 0;
+    int table_bt = -1;
     bool alive = true;  // warp-uniform; once false the remaining tiles are walked without waiting or computing,
                         // so that all epilogue threads still meet at every named barrier
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       const int nt = tile / b_tiles, bt = tile % b_tiles;
-      // combined scales of this tile, sx[kb][column] = a_scale[m, kb] * w_scale[nt, kb]
-      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");  // previous tile's readers are done with sx
-      const float *wsc = p.w_scale + size_t(nt) * kblocks;
-      for (int i = et; i < kblocks * kCols; i += kEpiThreads) {
-        const int kb = i / kCols, col = i % kCols, m = bt * kCols + col;
-        sx[i] = m < p.M ? __ldg(p.a_scale + size_t(m) * kblocks + kb) * __ldg(wsc + kb) : 0.f;
+      if (bt != table_bt) {  // activation scales of this batch tile: sa[kb][row] (a grid that is a multiple of b_tiles
+                             // keeps bt fixed per CTA, so this normally happens once)
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiActive) : "memory");  // readers of the previous table are done
+        for (int i = et; i < kblocks * kRows; i += kEpiActive) {
+          const int r = i / kblocks, kb = i % kblocks, m = bt * kRows + r;
+          sa[kb * kRows + r] = m < p.M ? __ldg(p.a_scale + size_t(m) * kblocks + kb) : 0.f;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiActive) : "memory");
+        table_bt = bt;
       }
-      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+      const float *wsc = p.w_scale + size_t(nt) * kblocks;
       float sum[kMyCols];
 #pragma unroll
       for (int c = 0; c < kMyCols; ++c) sum[c] = 0.f;
+      float w_next = __ldg(wsc);
       for (int kb = 0; kb < kblocks && alive; ++kb) {
         alive = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], acc_phase, ab));
         if (!alive) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t taddr = tmem_base + acc * kCols + col0 + (uint32_t(quad * 32) << 16);
-        const float4 *sxk = reinterpret_cast<const float4 *>(sx + kb * kCols + col0);
-        if constexpr (kMyCols == 16) {
-          uint32_t r[32];
-          tmem_ld16(taddr, r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-          for (int c = 0; c < 16; c += 4) {
-            const float4 sc = sxk[c >> 2];
-            sum[c] = fmaf(__uint_as_float(r[c]), sc.x, sum[c]);
-            sum[c + 1] = fmaf(__uint_as_float(r[c + 1]), sc.y, sum[c + 1]);
-            sum[c + 2] = fmaf(__uint_as_float(r[c + 2]), sc.z, sum[c + 2]);
-            sum[c + 3] = fmaf(__uint_as_float(r[c + 3]), sc.w, sum[c + 3]);
-          }
-        } else {
-#pragma unroll
-          for (int c0 = 0; c0 < kMyCols; c0 += 32) {
-            uint32_t r[32];
-            tmem_ld32(taddr + c0, r);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-            for (int c = 0; c < 32; c += 4) {
-              const float4 sc = sxk[(c0 + c) >> 2];
-              sum[c0 + c] = fmaf(__uint_as_float(r[c]), sc.x, sum[c0 + c]);
-              sum[c0 + c + 1] = fmaf(__uint_as_float(r[c + 1]), sc.y, sum[c0 + c + 1]);
-              sum[c0 + c + 2] = fmaf(__uint_as_float(r[c + 2]), sc.z, sum[c0 + c + 2]);
-              sum[c0 + c + 3] = fmaf(__uint_as_float(r[c + 3]), sc.w, sum[c0 + c + 3]);
-            }
-          }
-        }
+        uint32_t r[32];
+        tmem_ld32(lane_base + acc * kTileN, r);
+        const float scale = sa[kb * kRows + (row < kRows ? row : 0)] * w_next;
+        if (kb + 1 < kblocks) w_next = __ldg(wsc + kb + 1);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        // the values are in registers: the accumulator can be refilled while they are scaled and added
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[acc]);
         if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1; }
-      }
-      if (alive) {
-        const int n = nt * kTileN + quad * 32 + lane;
-        if (n < p.N) {
 #pragma unroll
-          for (int c = 0; c < kMyCols; ++c) {
-            const int m = bt * kCols + col0 + c;
-            if (m < p.M) {
-              if (p.rows_per_owner == 0) {
-                p.logits[size_t(m) * p.ldl + n] = sum[c];
-              } else {
-                const int owner = m / p.rows_per_owner;
-                p.owner_base[owner][size_t(m - owner * p.rows_per_owner) * p.ldl + p.col_offset + n] = sum[c];
-              }
-            }
-          }
+        for (int c = 0; c < kMyCols; ++c) sum[c] = fmaf(__uint_as_float(r[c]), scale, sum[c]);
+      }
+      const int m = bt * kRows + row, n0 = nt * kTileN + group * kMyCols;
+      if (alive && row < kRows && m < p.M && n0 < p.N) {
+        float *dst;
+        if (p.rows_per_owner == 0) {
+          dst = p.logits + size_t(m) * p.ldl + n0;
+        } else {
+          const int owner = m / p.rows_per_owner;
+          dst = p.owner_base[owner] + size_t(m - owner * p.rows_per_owner) * p.ldl + p.col_offset + n0;
+        }
+        if (n0 + kMyCols <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+          for (int c = 0; c < kMyCols; c += 4)
+            *reinterpret_cast<float4 *>(dst + c) = make_float4(sum[c], sum[c + 1], sum[c + 2], sum[c + 3]);
+        } else {
+#pragma unroll
+          for (int c = 0; c < kMyCols; ++c)
+            if (n0 + c < p.N) dst[c] = sum[c];
         }
       }
     }
@@ -342,36 +364,44 @@ EncodeFn encoder() {
   }();
   return fn;
 }
-// 2-D uint8 tensor [rows, cols] row-major, box [box_rows, 128 bytes], 128-byte swizzle, zero fill outside.
-bool make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+// uint8 matrix [rows, cols] row-major seen as a 3-D tensor [cols/128][rows][128 bytes] (strides 128 and cols bytes),
+// box {128 bytes, box_rows, group}: one copy brings `group` consecutive K blocks of box_rows rows, laid out in shared
+// memory as `group` K-major tiles of box_rows x 128 bytes with the 128-byte swizzle, and reads every row of the matrix
+// in runs of group*128 contiguous bytes.  Zero fill outside.
+bool make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t group) {
   EncodeFn enc = encoder();
   if (!enc) return false;
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols};
-  const cuuint32_t box[2] = {uint32_t(kTileK), box_rows};
-  const cuuint32_t elem[2] = {1, 1};
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, elem,
+  const cuuint64_t dims[3] = {uint64_t(kTileK), rows, cols / kTileK};
+  const cuuint64_t strides[2] = {cols, uint64_t(kTileK)};
+  const cuuint32_t box[3] = {uint32_t(kTileK), box_rows, group};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims, strides, box, elem,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int kCols, int kGroups>
+template <int kRows>
 cudaError_t launch_head(const CUtensorMap &mw, const CUtensorMap &ma, const HeadArgs &p, int sms, cudaStream_t stream) {
-  constexpr int kStages = HeadSmem<kCols>::kStages;
-  const size_t smem = 1024 + size_t(kStages) * HeadSmem<kCols>::kStageBytes + size_t(p.K / kTileK) * kCols * 4 +
-                      (2 * kStages + 2 * kAccBufs) * 8 + 16;
+  const int stages = HeadSmem<kRows>::stages(p.K / kTileK, p.group);
+  if (stages < 2) return cudaErrorInvalidValue;
+  const size_t smem = HeadSmem<kRows>::fixed_bytes(p.K / kTileK) + size_t(stages) * HeadSmem<kRows>::kStageBytes * p.group;
+  HeadArgs q = p;
+  q.stages = stages;
   static thread_local int configured = -1;
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (configured != dev) {
-    e = cudaFuncSetAttribute(head_fp8_kernel<kCols, kGroups>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    e = cudaFuncSetAttribute(head_fp8_kernel<kRows>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     configured = dev;
   }
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
-  const int tiles = ((p.N + kTileN - 1) / kTileN) * ((p.M + kCols - 1) / kCols);
-  head_fp8_kernel<kCols, kGroups><<<tiles < sms ? tiles : sms, 64 + 128 * kGroups, smem, stream>>>(mw, ma, p);
+  const int b_tiles = (p.M + kRows - 1) / kRows;
+  const int tiles = ((p.N + kTileN - 1) / kTileN) * b_tiles;
+  int grid = tiles < sms ? tiles : sms;
+  if (b_tiles <= grid) grid -= grid % b_tiles;  // every CTA then keeps one batch tile (and its scale table) for good
+  head_fp8_kernel<kRows><<<grid, kHeadThreads, smem, stream>>>(mw, ma, q);
   return cudaGetLastError();
 }
 
@@ -437,14 +467,30 @@ int run_head(const void *a_e4m3, const float *a_scale, const void *w_e4m3, const
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (e != cudaSuccess) return int(e);
   const int cols = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+  // K blocks per stage: the largest of 4, 2, 1 that divides K/128 and still leaves a ring of at least 2 stages
+  // (measured: longer contiguous runs per weight row beat a deeper ring of shorter ones)
+  const int kblocks = K / kTileK;
+  auto ring = [&](int g) {
+    return cols == 16 ? HeadSmem<16>::stages(kblocks, g) : cols == 32 ? HeadSmem<32>::stages(kblocks, g)
+         : cols == 64 ? HeadSmem<64>::stages(kblocks, g) : HeadSmem<128>::stages(kblocks, g);
+  };
+  int group = 1;
+  for (int g = 4; g > 1; g >>= 1)
+    if (kblocks % g == 0 && ring(g) >= 2) { group = g; break; }
+  if (const char *forced = getenv("DS41_HEAD_GROUP")) {
+    const int g = atoi(forced);
+    if ((g == 1 || g == 2 || g == 4) && kblocks % g == 0 && ring(g) >= 2) group = g;
+  }
+  p.group = group;
   CUtensorMap mw, ma;
-  if (!make_map(&mw, w_e4m3, uint64_t(N), uint64_t(K), kTileN) || !make_map(&ma, a_e4m3, uint64_t(M), uint64_t(K), uint32_t(cols)))
+  if (!make_map(&mw, w_e4m3, uint64_t(N), uint64_t(K), kTileN, uint32_t(group)) ||
+      !make_map(&ma, a_e4m3, uint64_t(M), uint64_t(K), uint32_t(cols), uint32_t(group)))
     return invalid("cuTensorMapEncodeTiled failed");
   switch (cols) {
-    case 16: e = launch_head<16, 1>(mw, ma, p, sms, stream); break;
-    case 32: e = launch_head<32, 1>(mw, ma, p, sms, stream); break;
-    case 64: e = launch_head<64, 1>(mw, ma, p, sms, stream); break;
-    default: e = launch_head<128, 2>(mw, ma, p, sms, stream); break;
+    case 16: e = launch_head<16>(mw, ma, p, sms, stream); break;
+    case 32: e = launch_head<32>(mw, ma, p, sms, stream); break;
+    case 64: e = launch_head<64>(mw, ma, p, sms, stream); break;
+    default: e = launch_head<128>(mw, ma, p, sms, stream); break;
   }
   return int(e);
 }
