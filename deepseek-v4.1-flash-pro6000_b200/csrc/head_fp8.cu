@@ -295,23 +295,52 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
         for (int c = 0; c < kMyCols; ++c) sum[c] = fmaf(__uint_as_float(r[c]), scale, sum[c]);
       }
-      const int m = bt * kRows + row, n0 = nt * kTileN + group * kMyCols;
-      if (alive && row < kRows && m < p.M && n0 < p.N) {
-        float *dst;
-        if (p.rows_per_owner == 0) {
-          dst = p.logits + size_t(m) * p.ldl + n0;
-        } else {
-          const int owner = m / p.rows_per_owner;
-          dst = p.owner_base[owner] + size_t(m - owner * p.rows_per_owner) * p.ldl + p.col_offset + n0;
+      // Output.  Lane l holds row l of the warp's 32 x 32 block.  Written as it is, one store instruction would touch
+      // 32 rows with 16 bytes each; an 8 x 8 transpose of the 16-byte column groups across the lanes that share
+      // l % 4 (butterflies at lane distances 4, 8, 16) turns that into 4 rows with 128 contiguous bytes each, which is
+      // what a peer GPU's memory wants to be written with (and the local L2 as well).
+      if (alive) {
+        float4 x[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) x[c] = make_float4(sum[4 * c], sum[4 * c + 1], sum[4 * c + 2], sum[4 * c + 3]);
+#pragma unroll
+        for (int s3 = 0; s3 < 3; ++s3) {
+          const int dist = 4 << s3;
+          const bool upper = (lane >> (2 + s3)) & 1;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            if ((c >> s3) & 1) continue;
+            const int c2 = c | (1 << s3);
+            const float4 give = upper ? x[c] : x[c2];
+            float4 take;
+            take.x = __shfl_xor_sync(0xffffffffu, give.x, dist);
+            take.y = __shfl_xor_sync(0xffffffffu, give.y, dist);
+            take.z = __shfl_xor_sync(0xffffffffu, give.z, dist);
+            take.w = __shfl_xor_sync(0xffffffffu, give.w, dist);
+            if (upper) x[c] = take; else x[c2] = take;
+          }
         }
-        if (n0 + kMyCols <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+        // now x[a] = columns [4*(lane/4), +4) of block row 4*a + lane%4
+        const int n = nt * kTileN + group * kMyCols + 4 * (lane >> 2);
 #pragma unroll
-          for (int c = 0; c < kMyCols; c += 4)
-            *reinterpret_cast<float4 *>(dst + c) = make_float4(sum[c], sum[c + 1], sum[c + 2], sum[c + 3]);
-        } else {
+        for (int a8 = 0; a8 < 8; ++a8) {
+          const int r = quad * 32 + 4 * a8 + (lane & 3), m = bt * kRows + r;
+          if (r >= kRows || m >= p.M || n >= p.N) continue;
+          float *dst;
+          if (p.rows_per_owner == 0) {
+            dst = p.logits + size_t(m) * p.ldl + n;
+          } else {
+            const int owner = m / p.rows_per_owner;
+            dst = p.owner_base[owner] + size_t(m - owner * p.rows_per_owner) * p.ldl + p.col_offset + n;
+          }
+          if (n + 4 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+            *reinterpret_cast<float4 *>(dst) = x[a8];
+          } else {
+            const float v[4] = {x[a8].x, x[a8].y, x[a8].z, x[a8].w};
 #pragma unroll
-          for (int c = 0; c < kMyCols; ++c)
-            if (n0 + c < p.N) dst[c] = sum[c];
+            for (int k = 0; k < 4; ++k)
+              if (n + k < p.N) dst[k] = v[k];
+          }
         }
       }
     }
