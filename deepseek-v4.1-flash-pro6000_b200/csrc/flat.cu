@@ -1,0 +1,532 @@
+// Batch path of the sampler for WIDE nuclei (flat distributions) at batch sizes where a thread-block cluster per row
+// leaves the GPU idle most of the time: the wide-nucleus algorithm of row_wide.cuh restated as five grid-wide kernels
+// over the whole batch, so that every pass runs at full occupancy.
+//   flat_stats_kernel   (row, quarter row)  maximum (first), minimum, finiteness                         -> FlatPartial
+//   flat_hist_kernel    (row, quarter row)  1024-bin histogram over the row's range: exact counts and fixed-point
+//                                           FP32-class masses, shared memory first, then global integer atomics
+//   flat_window_kernel  (row)               error-bracketed running mass -> the window of bins that holds the top-p
+//                                           crossing; rows this path does not fit get status -8 (the caller sends
+//                                           them to the other paths), non-finite rows -1
+//   flat_mass_kernel    (row, quarter row)  the one FP64 pass: per 1024-id sub-region the normaliser part, the mass
+//                                           and count of the ids before the window; the window's ids to a per-row list
+//   flat_resolve_kernel (row)               sorts the list exactly, FP64 prefix sums -> certified cut; kept mass per
+//                                           sub-region -> the sub-region that holds u * total -> walks its 1024 ids
+// Rule, error bounds and status words are those of the cluster kernel (row_kernel.cuh, row_wide.cuh); the reference
+// rule is engine/third_party/spark/src/sampling.cpp:18-38.
+#include "flat.cuh"
+
+#include "row_core.cuh"
+
+namespace ds41 {
+namespace {
+
+constexpr int kFT = kFlatThreads;
+constexpr int kFW = kFT / 32;
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+struct FlatRed {  // per-CTA scratch for block reductions / prefix sums
+  double d[kFW], e[kFW];
+  float f[kFW], g[kFW];
+  int i[kFW], j[kFW];
+};
+
+// Inclusive prefix over 2 * kFT values, two consecutive per thread; returns the prefix through v0.
+__device__ __forceinline__ double flat_prefix2(FlatRed &r, double v0, double v1) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  double scan = v0 + v1;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const double up = __shfl_up_sync(0xffffffffu, scan, o);
+    if (lane >= o) scan += up;
+  }
+  if (lane == 31) r.d[warp] = scan;
+  __syncthreads();
+  double base = 0;
+  for (int w = 0; w < warp; ++w) base += r.d[w];
+  __syncthreads();
+  return base + scan - v1;
+}
+__device__ __forceinline__ int flat_sum(FlatRed &r, int v) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = __reduce_add_sync(0xffffffffu, v);
+  if (lane == 0) r.i[warp] = v;
+  __syncthreads();
+  int t = 0;
+  for (int w = 0; w < kFW; ++w) t += r.i[w];
+  __syncthreads();
+  return t;
+}
+__device__ __forceinline__ double flat_sum(FlatRed &r, double v) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if (lane == 0) r.d[warp] = v;
+  __syncthreads();
+  double t = 0;
+  for (int w = 0; w < kFW; ++w) t += r.d[w];
+  __syncthreads();
+  return t;
+}
+
+// ids [begin, end) of this CTA's quarter row
+__device__ __forceinline__ void quarter(const FlatArgs &a, int chunk, int *begin, int *end) {
+  *begin = min(a.vocab, chunk * kFlatChunkIds);
+  *end = min(a.vocab, *begin + kFlatChunkIds);
+}
+
+__global__ void __launch_bounds__(kFT) flat_stats_kernel(FlatArgs a) {
+  __shared__ FlatRed red;
+  const int row = blockIdx.x / kFlatChunks, chunk = blockIdx.x % kFlatChunks;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int begin, end;
+  quarter(a, chunk, &begin, &end);
+  const float *x = a.logits + size_t(row) * a.stride;
+  float best = -CUDART_INF_F, lowest = CUDART_INF_F;
+  int best_id = 0x7fffffff, flags = 0;
+  auto take = [&](float v, int id) {
+    if ((__float_as_uint(v) & 0x7f800000u) == 0x7f800000u) flags = 1;
+    if (v > best) { best = v; best_id = id; }
+    lowest = fminf(lowest, v);
+  };
+  const int vec_end = begin + ((end - begin) & ~3);  // begin is a multiple of 4, rows are 16-byte aligned
+  for (int i = begin + 4 * threadIdx.x; i < vec_end; i += 4 * kFT) {
+    const float4 v = __ldg(reinterpret_cast<const float4 *>(x + i));
+    take(v.x, i); take(v.y, i + 1); take(v.z, i + 2); take(v.w, i + 3);
+  }
+  for (int i = vec_end + threadIdx.x; i < end; i += kFT) take(__ldg(x + i), i);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_id, o);
+    if (ov > best || (ov == best && oi < best_id)) { best = ov; best_id = oi; }
+    lowest = fminf(lowest, __shfl_xor_sync(0xffffffffu, lowest, o));
+  }
+  flags = int(__reduce_or_sync(0xffffffffu, unsigned(flags)));
+  if (lane == 0) { red.f[warp] = best; red.i[warp] = best_id; red.g[warp] = lowest; red.j[warp] = flags; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < kFW; ++w) {
+      if (red.f[w] > best || (red.f[w] == best && red.i[w] < best_id)) { best = red.f[w]; best_id = red.i[w]; }
+      lowest = fminf(lowest, red.g[w]);
+      flags |= red.j[w];
+    }
+    a.s.partial[row * kFlatChunks + chunk] = FlatPartial{best, lowest, best_id, flags};
+  }
+}
+
+// Row maximum (first), minimum and flags from the quarter rows' partial results; the same in every thread.
+__device__ __forceinline__ FlatPartial row_extremes(const FlatArgs &a, int row) {
+  FlatPartial r = a.s.partial[row * kFlatChunks];
+  for (int c = 1; c < kFlatChunks; ++c) {
+    const FlatPartial p = a.s.partial[row * kFlatChunks + c];
+    if (p.max > r.max || (p.max == r.max && p.argmax < r.argmax)) { r.max = p.max; r.argmax = p.argmax; }
+    r.min = fminf(r.min, p.min);
+    r.flags |= p.flags;
+  }
+  return r;
+}
+
+struct FlatBins {  // binning of one row: bin = min(1023, int((max - y) * inv_w))
+  float m, range, inv_w, c32, step;
+};
+__device__ __forceinline__ FlatBins make_bins(const FlatPartial &e, double t) {
+  FlatBins b;
+  b.m = e.max;
+  b.c32 = float(1.4426950408889634074 / t);
+  b.range = (e.max - e.min) * 1.0001f + 1e-30f;
+  b.inv_w = float(kFlatBins) / b.range;
+  b.step = b.range / float(kFlatBins) * b.c32;  // bin width in units of the exponent of 2
+  return b;
+}
+
+__global__ void __launch_bounds__(kFT) flat_hist_kernel(FlatArgs a) {
+  __shared__ unsigned count[kFlatBins], qmass[kFlatBins];
+  const int row = blockIdx.x / kFlatChunks, chunk = blockIdx.x % kFlatChunks;
+  const FlatPartial ext = row_extremes(a, row);
+  if (ext.flags || !(ext.min < ext.max)) return;  // the window kernel reports the row
+  const FlatBins b = make_bins(ext, a.t);
+  for (int j = threadIdx.x; j < kFlatBins; j += kFT) { count[j] = 0u; qmass[j] = 0u; }
+  __syncthreads();
+  int begin, end;
+  quarter(a, chunk, &begin, &end);
+  const float *x = a.logits + size_t(row) * a.stride;
+  // an id of bin k adds round(2^20 * w / 2^-(k*step)), a number in (2^19, 2^20]: integer atomics accumulate it exactly
+  auto take = [&](float y) {
+    const float d = b.m - y;
+    const int k = min(kFlatBins - 1, int(d * b.inv_w));
+    atomicAdd(&count[k], 1u);
+    atomicAdd(&qmass[k], __float2uint_rn(1048576.f * ex2_approx(fmaf(float(k), b.step, -(d * b.c32)))));
+  };
+  const int vec_end = begin + ((end - begin) & ~3);
+  for (int i = begin + 4 * threadIdx.x; i < vec_end; i += 4 * kFT) {
+    const float4 v = __ldg(reinterpret_cast<const float4 *>(x + i));
+    take(v.x); take(v.y); take(v.z); take(v.w);
+  }
+  for (int i = vec_end + threadIdx.x; i < end; i += kFT) take(__ldg(x + i));
+  __syncthreads();
+  bool crowded = false;  // 4096 or more ids of this quarter row in one bin: the 32-bit mass may have wrapped
+  for (int j = threadIdx.x; j < kFlatBins; j += kFT) {
+    const unsigned n = count[j];
+    if (n) {
+      atomicAdd(&a.s.hcount[size_t(row) * kFlatBins + j], n);
+      atomicAdd(&a.s.hmass[size_t(row) * kFlatBins + j], (unsigned long long)qmass[j]);
+      crowded |= n >= 4096u;
+    }
+  }
+  if (crowded) atomicOr(&a.s.lcount[row * 4 + 1], 1);
+}
+
+__global__ void __launch_bounds__(kFT) flat_window_kernel(FlatArgs a) {
+  __shared__ FlatRed red;
+  __shared__ int first[2];
+  __shared__ double totals[2];
+  const int row = blockIdx.x;
+  const FlatPartial ext = row_extremes(a, row);
+  FlatInfo info{};
+  info.max = ext.max; info.min = ext.min; info.argmax = ext.argmax;
+  if (ext.flags) {  // same answer in every thread
+    if (threadIdx.x == 0) {
+      a.s.info[row] = info;
+      a.tokens[row] = -1;
+      a.status[row] = -1;
+    }
+    return;
+  }
+  const FlatBins b = make_bins(ext, a.t);
+  int cnt[2] = {0, 0};
+  double lo[2] = {0, 0}, hi[2] = {0, 0};
+  if (ext.min < ext.max) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int k = 2 * threadIdx.x + i;
+      cnt[i] = int(a.s.hcount[size_t(row) * kFlatBins + k]);
+      const unsigned long long q = a.s.hmass[size_t(row) * kFlatBins + k];
+      // error of the measured mass of a bin: see row_wide.cuh (the arithmetic per id is the same)
+      const double x_far = (double(k) + 1.0) * double(b.step) * 1.0001;
+      const double e = (5.6 * x_far + 41.0) * 5.9604644775390625e-8;
+      const double mass = double(q) * 9.5367431640625e-7 * exp2(-double(float(k) * b.step));
+      lo[i] = mass * (1.0 - e); hi[i] = mass * (1.0 + e);
+    }
+  }
+  const double lo0 = flat_prefix2(red, lo[0], lo[1]), hi0 = flat_prefix2(red, hi[0], hi[1]);
+  if (threadIdx.x == kFT - 1) { totals[0] = lo0 + lo[1]; totals[1] = hi0 + hi[1]; }
+  if (threadIdx.x == 0) { first[0] = 0x7fffffff; first[1] = 0x7fffffff; }
+  __syncthreads();
+  const double t_lo = a.top_p * totals[0] * (1.0 - 1e-12), t_hi = a.top_p * totals[1] * (1.0 + 1e-12);
+  // w0: first bin through which the running mass MAY reach the target; w1: first through which it SURELY does
+  if (hi0 >= t_lo) atomicMin(&first[0], 2 * threadIdx.x); else if (hi0 + hi[1] >= t_lo) atomicMin(&first[0], 2 * threadIdx.x + 1);
+  if (lo0 >= t_hi) atomicMin(&first[1], 2 * threadIdx.x); else if (lo0 + lo[1] >= t_hi) atomicMin(&first[1], 2 * threadIdx.x + 1);
+  __syncthreads();
+  const int w0 = first[0], w1 = first[1];
+  const bool found = w0 != 0x7fffffff && w1 != 0x7fffffff && w1 >= w0;
+  int through = 0, inside = 0;
+  if (found) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int k = 2 * threadIdx.x + i;
+      if (k <= w1) { through += cnt[i]; if (k >= w0) inside += cnt[i]; }
+    }
+  }
+  through = flat_sum(red, through);
+  inside = flat_sum(red, inside);
+  const bool crowded = a.s.lcount[row * 4 + 1] != 0;
+  // this path's case: a window exists, the nucleus is wide (a small one is the other paths' case), the window fits
+  // the list, no mass wrapped
+  const bool ok = found && through > kFlatMinNucleus && inside <= kFlatList && !crowded;
+  if (threadIdx.x == 0) {
+    info.applicable = ok ? 1 : 0; info.w0 = w0; info.w1 = w1;
+    a.s.info[row] = info;
+    if (!ok) { a.tokens[row] = -1; a.status[row] = -8; }
+  }
+}
+
+__global__ void __launch_bounds__(kFT) flat_mass_kernel(FlatArgs a) {
+  const int row = blockIdx.x / kFlatChunks, chunk = blockIdx.x % kFlatChunks;
+  const FlatInfo info = a.s.info[row];
+  if (!info.applicable) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  FlatPartial ext{info.max, info.min, info.argmax, 0};
+  const FlatBins b = make_bins(ext, a.t);
+  const float edge0 = float(info.w0), edge1 = info.w1 >= kFlatBins - 1 ? CUDART_INF_F : float(info.w1 + 1);
+  const double inv_t = 1.0 / a.t, m64 = double(info.max);
+  const float *x = a.logits + size_t(row) * a.stride;
+  constexpr int kSubsPerWarp = kFlatSubs / kFlatChunks / kFW;  // 2
+#pragma unroll 1
+  for (int s = 0; s < kSubsPerWarp; ++s) {
+    const int sub = chunk * (kFlatSubs / kFlatChunks) + warp * kSubsPerWarp + s;
+    const int base = sub * kFlatSub;
+    double z = 0, sure_mass = 0;
+    int sure_count = 0;
+    for (int it = 0; it < kFlatSub; it += 32) {
+      const int id = base + it + lane;
+      bool inside = false;
+      float y = 0.f;
+      if (id < a.vocab) {
+        y = __ldg(x + id);
+        const double e = exp_nonpos((double(y) - m64) * inv_t);
+        z += e;
+        // bin(y) < w0 and bin(y) <= w1 without forming the bin: int(v) < k is v < k for v >= 0
+        const float v = (b.m - y) * b.inv_w;
+        const bool sure = v < edge0;
+        if (sure) { sure_mass += e; ++sure_count; }
+        inside = !sure && v < edge1;
+      }
+      const unsigned ballot = __ballot_sync(0xffffffffu, inside);
+      if (ballot) {
+        int slot0 = 0;
+        if (lane == 0) slot0 = atomicAdd(&a.s.lcount[row * 4], __popc(ballot));
+        slot0 = __shfl_sync(0xffffffffu, slot0, 0);
+        if (inside) {
+          const int slot = slot0 + __popc(ballot & ((1u << lane) - 1u));
+          // ascending 64-bit key = (logit descending, id ascending); +0 and -0 compare equal as logits: both map to +0
+          const float yy = y == 0.f ? 0.f : y;
+          const uint32_t bits = __float_as_uint(yy), ordered = bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u);
+          if (slot < kFlatList) a.s.lkeys[size_t(row) * kFlatList + slot] = (unsigned long long)(~ordered) << 32 | uint32_t(id);
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      z += __shfl_xor_sync(0xffffffffu, z, o);
+      sure_mass += __shfl_xor_sync(0xffffffffu, sure_mass, o);
+    }
+    sure_count = __reduce_add_sync(0xffffffffu, sure_count);
+    if (lane == 0) {
+      a.s.subz[size_t(row) * kFlatSubs + sub] = z;
+      a.s.subsure[size_t(row) * kFlatSubs + sub] = sure_mass;
+      a.s.subcnt[size_t(row) * kFlatSubs + sub] = sure_count;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
+  __shared__ FlatRed red;
+  __shared__ unsigned long long keys[kFlatList];
+  __shared__ double ksum[kFlatSubs];
+  __shared__ int found_at;
+  __shared__ double cut_mass[2];
+  __shared__ float cut_y;
+  __shared__ int cut_id, cut_amb;
+  const int row = blockIdx.x;
+  const FlatInfo info = a.s.info[row];
+  if (!info.applicable) return;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const double inv_t = 1.0 / a.t, m64 = double(info.max);
+  const float *x = a.logits + size_t(row) * a.stride;
+  const int listed = a.s.lcount[row * 4];
+  // normaliser, mass and count before the window: fixed order (sub-regions across threads, then the block tree)
+  double z = 0, mass_before = 0;
+  int n_before = 0;
+  if (tid < kFlatSubs) {
+    z = a.s.subz[size_t(row) * kFlatSubs + tid];
+    mass_before = a.s.subsure[size_t(row) * kFlatSubs + tid];
+    n_before = a.s.subcnt[size_t(row) * kFlatSubs + tid];
+    ksum[tid] = mass_before;
+  }
+  z = flat_sum(red, z);
+  mass_before = flat_sum(red, mass_before);
+  n_before = flat_sum(red, n_before);
+  bool ok = listed >= 1 && listed <= kFlatList;
+  const int n = ok ? listed : 0;
+  int padded = 64;
+  while (padded < n) padded <<= 1;
+  for (int i = tid; i < padded; i += kFT) keys[i] = i < n ? a.s.lkeys[size_t(row) * kFlatList + i] : ~0ull;
+  __syncthreads();
+  if (padded <= kFT) {
+    // bitonic network, one key per thread: partners closer than a warp exchange by shuffle, the others through
+    // shared memory
+    unsigned long long key = tid < padded ? keys[tid] : ~0ull;
+    for (int k = 2; k <= padded; k <<= 1) {
+      for (int jj = k >> 1; jj > 0; jj >>= 1) {
+        unsigned long long other;
+        if (jj < 32) {
+          other = __shfl_xor_sync(0xffffffffu, key, jj);
+        } else {
+          keys[tid] = key;
+          __syncthreads();
+          other = keys[tid ^ jj];
+          __syncthreads();
+        }
+        const bool keep_min = ((tid & jj) == 0) == ((tid & k) == 0);
+        key = keep_min ? (key < other ? key : other) : (key < other ? other : key);
+      }
+    }
+    keys[tid] = key;
+    __syncthreads();
+  } else {
+    for (int k = 2; k <= padded; k <<= 1) {
+      for (int jj = k >> 1; jj > 0; jj >>= 1) {
+        for (int i = tid; i < padded / 2; i += kFT) {
+          const int lo_i = ((i / jj) * 2 * jj) + (i % jj), hi_i = lo_i + jj;
+          const bool up = (lo_i & k) == 0;
+          const unsigned long long p = keys[lo_i], q = keys[hi_i];
+          if ((p > q) == up) { keys[lo_i] = q; keys[hi_i] = p; }
+        }
+        __syncthreads();
+      }
+    }
+  }
+  // FP64 weights in sorted order and their prefix sums from the mass before the window
+  double e[2];
+  float ys[2];
+  int ids[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = 2 * tid + i;
+    const unsigned long long key = r < n ? keys[r] : 0ull;
+    const uint32_t ordered = r < n ? ~uint32_t(key >> 32) : 0x80000000u;
+    ys[i] = __uint_as_float(ordered ^ ((ordered >> 31) ? 0x80000000u : 0xffffffffu));
+    ids[i] = int(uint32_t(key));
+    e[i] = r < n ? exp_nonpos((double(ys[i]) - m64) * inv_t) : 0.0;
+  }
+  const double through0 = mass_before + flat_prefix2(red, e[0], e[1]), through1 = through0 + e[1];
+  const double rel = 2.0 * (double(a.vocab) + 256.0) * kU;
+  const double target_p = a.top_p * z, lo = target_p * (1.0 - rel), hi = target_p * (1.0 + rel);
+  if (tid == 0) found_at = 0x7fffffff;
+  __syncthreads();
+  {
+    int mine = -1;
+    if (2 * tid < n && through0 >= target_p) mine = 2 * tid;
+    else if (2 * tid + 1 < n && through1 >= target_p) mine = 2 * tid + 1;
+    if (mine >= 0) atomicMin(&found_at, mine);
+  }
+  __syncthreads();
+  const int pos = found_at;
+  // mass_before >= lo: the crossing is (or may be) before the window; pos unset: not reached inside it
+  ok = ok && mass_before < lo && pos != 0x7fffffff;
+  if (!ok) {  // uniform in the CTA: the other paths redo the row
+    if (tid == 0) { a.tokens[row] = -1; a.status[row] = -8; }
+    return;
+  }
+  if ((pos >> 1) == tid) {
+    const int i = pos & 1;
+    const double mass_at = i ? through1 : through0, prev_at = mass_at - e[i];
+    cut_amb = ((mass_at < hi) || (prev_at >= lo)) ? 1 : 0;
+    cut_y = ys[i]; cut_id = ids[i];
+    cut_mass[0] = mass_at;
+  }
+  __syncthreads();
+  // kept mass per sub-region: the ids before the window plus the window's ids up to the cut
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+    if (2 * tid + i <= pos) atomicAdd(&ksum[ids[i] / kFlatSub], e[i]);
+  __syncthreads();
+  const Cut cut{cut_y, cut_id};
+  const int kept = n_before + pos + 1;
+  int status = cut_amb ? 2 : 0;
+  // ---- inverse CDF in id order (sampling.cpp:18-21): sub-region that holds u * total, then its ids one by one
+  const double k0 = tid < kFlatSubs / 2 ? ksum[2 * tid] : 0.0, k1 = tid < kFlatSubs / 2 ? ksum[2 * tid + 1] : 0.0;
+  const double pre0 = flat_prefix2(red, k0, k1), pre1 = pre0 + k1;  // kept mass through sub-region 2*tid (and 2*tid+1)
+  if (tid == kFT - 1) cut_mass[1] = pre1;  // total (threads beyond the sub-regions add zeros)
+  if (tid == 0) found_at = 0x7fffffff;
+  __syncthreads();
+  const double total = cut_mass[1];
+  const double u = philox_uniform(a.seeds[row], a.steps[row], a.slot, a.purpose);
+  const double target = u * total, slack = (2.0 * kept + 512.0) * kU * total;
+  if (tid < kFlatSubs / 2) {
+    int mine = -1;
+    if (k0 > 0 && target < pre0) mine = 2 * tid;
+    else if (k1 > 0 && target < pre1) mine = 2 * tid + 1;
+    if (mine >= 0) atomicMin(&found_at, mine);
+  }
+  __syncthreads();
+  int sub = found_at;
+  bool amb = false;
+  if (sub == 0x7fffffff) {  // target >= total by rounding: the last sub-region with kept mass, flagged
+    amb = true;
+    if (tid == 0) found_at = -1;
+    __syncthreads();
+    if (tid < kFlatSubs && ksum[tid] > 0) atomicMax(&found_at, tid);
+    __syncthreads();
+    sub = found_at;
+  }
+  if (sub < 0) {  // cannot happen (the maximum has weight 1): leave the row to the other paths
+    if (tid == 0) { a.tokens[row] = -1; a.status[row] = -8; }
+    return;
+  }
+  // kept mass before the sub-region, as the prefix above saw it
+  __syncthreads();
+  if ((sub >> 1) == tid) cut_mass[0] = (sub & 1) ? pre0 : pre0 - k0;
+  if (tid == 0) found_at = 0x7fffffff;
+  __syncthreads();
+  const double carry = cut_mass[0];
+  double v[2];
+  int vid[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    vid[i] = sub * kFlatSub + 2 * tid + i;
+    const bool in = vid[i] < a.vocab;
+    const float y = in ? __ldg(x + vid[i]) : -CUDART_INF_F;
+    const double w = exp_nonpos((double(y) - m64) * inv_t);
+    v[i] = (in && survives(y, vid[i], cut)) ? w : 0.0;
+  }
+  const double c0 = carry + flat_prefix2(red, v[0], v[1]), c1 = c0 + v[1];
+  {
+    int mine = -1;
+    if (v[0] > 0 && target < c0) mine = 2 * tid;
+    else if (v[1] > 0 && target < c1) mine = 2 * tid + 1;
+    if (mine >= 0) atomicMin(&found_at, mine);
+  }
+  __syncthreads();
+  const int hit = found_at;
+  if (hit == 0x7fffffff) {
+    // rounding left the target past the sub-region's last step: its last kept id, flagged (as the cluster kernel)
+    if (tid == 0) found_at = -1;
+    __syncthreads();
+    if (v[1] > 0) atomicMax(&found_at, 2 * tid + 1); else if (v[0] > 0) atomicMax(&found_at, 2 * tid);
+    __syncthreads();
+    if (tid == 0) {
+      a.tokens[row] = found_at >= 0 ? sub * kFlatSub + found_at : -1;
+      a.status[row] = found_at >= 0 ? (status | 1) : -8;
+    }
+    return;
+  }
+  if ((hit >> 1) == tid) {
+    const int i = hit & 1;
+    const double cum = i ? c1 : c0, below = cum - v[i];
+    if ((cum - target < slack) || (below > 0 && target - below < slack)) amb = true;
+    a.tokens[row] = vid[i];
+    a.status[row] = status | (amb ? 1 : 0);
+  }
+  (void)lane;
+}
+
+}  // namespace
+
+size_t flat_scratch_bytes(int rows) {
+  size_t per_row = kFlatChunks * sizeof(FlatPartial) + kFlatBins * (sizeof(unsigned) + sizeof(unsigned long long)) +
+                   sizeof(FlatInfo) + kFlatSubs * (2 * sizeof(double) + sizeof(int)) + 4 * sizeof(int) +
+                   kFlatList * sizeof(unsigned long long);
+  return size_t(rows) * per_row + 256;
+}
+
+cudaError_t launch_flat(FlatArgs a, void *scratch, cudaStream_t stream) {
+  // carve (every array is a multiple of 16 bytes per row; the zeroed ones come first, in one block)
+  unsigned char *p = static_cast<unsigned char *>(scratch);
+  const size_t rows = size_t(a.rows);
+  a.s.hmass = reinterpret_cast<unsigned long long *>(p); p += rows * kFlatBins * sizeof(unsigned long long);
+  a.s.hcount = reinterpret_cast<unsigned *>(p); p += rows * kFlatBins * sizeof(unsigned);
+  a.s.lcount = reinterpret_cast<int *>(p); p += rows * 4 * sizeof(int);
+  const size_t zeroed = size_t(p - static_cast<unsigned char *>(scratch));
+  a.s.lkeys = reinterpret_cast<unsigned long long *>(p); p += rows * kFlatList * sizeof(unsigned long long);
+  a.s.subz = reinterpret_cast<double *>(p); p += rows * kFlatSubs * sizeof(double);
+  a.s.subsure = reinterpret_cast<double *>(p); p += rows * kFlatSubs * sizeof(double);
+  a.s.info = reinterpret_cast<FlatInfo *>(p); p += rows * sizeof(FlatInfo);
+  a.s.partial = reinterpret_cast<FlatPartial *>(p); p += rows * kFlatChunks * sizeof(FlatPartial);
+  a.s.subcnt = reinterpret_cast<int *>(p);
+  cudaError_t e = cudaMemsetAsync(scratch, 0, zeroed, stream);
+  if (e != cudaSuccess) return e;
+  flat_stats_kernel<<<a.rows * kFlatChunks, kFT, 0, stream>>>(a);
+  flat_hist_kernel<<<a.rows * kFlatChunks, kFT, 0, stream>>>(a);
+  flat_window_kernel<<<a.rows, kFT, 0, stream>>>(a);
+  flat_mass_kernel<<<a.rows * kFlatChunks, kFT, 0, stream>>>(a);
+  flat_resolve_kernel<<<a.rows, kFT, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace ds41

@@ -2,6 +2,7 @@
 #include "ds41_b200.h"
 #include "row_kernel.cuh"
 #include "stream_types.cuh"
+#include "flat.cuh"
 #include "host_error.h"
 #include <cmath>
 
@@ -49,9 +50,17 @@ cudaError_t launch_combine(const CombineArgs &a, bool stats, cudaStream_t stream
 
 using namespace ds41;
 
+namespace {
+// [chunk records][status words when the caller passes none][batch path for wide nuclei]
+size_t streaming_bytes(int rows, int vocab) {
+  return size_t(rows) * chunks_for(vocab) * sizeof(ChunkRecord) + ((size_t(rows) * 4 + 15) & ~size_t(15));
+}
+bool flat_shape(int rows, int vocab) { return rows >= kFlatMinRows && vocab >= kFlatMinVocab; }
+}  // namespace
+
 extern "C" size_t ds41_b200_sample_scratch_bytes(int rows, int vocab) {
   if (rows < 1 || vocab < 1 || vocab > DS41_B200_MAX_VOCAB) return 0;
-  return size_t(rows) * chunks_for(vocab) * sizeof(ChunkRecord) + ((size_t(rows) * 4 + 15) & ~size_t(15));
+  return streaming_bytes(rows, vocab) + (flat_shape(rows, vocab) ? flat_scratch_bytes(rows) : 0);
 }
 
 extern "C" uint32_t ds41_spark_rng_word_v2(uint64_t seed, uint64_t step, uint32_t slot, uint32_t purpose, uint64_t draw) {
@@ -91,15 +100,28 @@ extern "C" int ds41_b200_sample_logits(const ds41_b200_sample_args *p, cudaStrea
                          !penalised && !p->mask && p->top_k <= kCand &&
                          (p->top_p < 1.0 || p->top_k > 0 || p->temperature == 0);  // a full-vocabulary draw is never covered
   if (!streaming) return int(launch_rows<kModeSample>(a, p->rows, stream));
-  // streaming path: chunk records -> combine -> cluster kernel only for the rows the combine could not cover
   const int chunks = chunks_for(p->vocab);
   ChunkRecord *records = static_cast<ChunkRecord *>(p->scratch);
   int32_t *status = p->status ? p->status : reinterpret_cast<int32_t *>(records + size_t(p->rows) * chunks);
-  ChunkArgs c{p->logits, p->logits_stride, p->vocab, 0, chunks, a.temperature, records};
-  cudaError_t e = launch_chunks(c, p->rows, stream);
+  cudaError_t e;
+  // Large batches of top-p rows first go through the batch path for wide nuclei; it answers the rows it fits and
+  // marks the others -8, and the paths below then only touch those.
+  const bool flat = flat_shape(p->rows, p->vocab) && p->top_k == 0 && p->top_p < 1.0 && p->temperature > 0 &&
+                    p->logits_stride != 0 && p->logits_stride % 4 == 0 && !(reinterpret_cast<uintptr_t>(p->logits) & 15u);
+  if (flat) {
+    FlatArgs f{};
+    f.logits = p->logits; f.stride = p->logits_stride; f.vocab = p->vocab; f.rows = p->rows;
+    f.t = a.temperature; f.top_p = p->top_p; f.seeds = p->seeds; f.steps = p->steps; f.slot = p->slot;
+    f.purpose = p->purpose; f.tokens = p->tokens; f.status = status;
+    e = launch_flat(f, static_cast<unsigned char *>(p->scratch) + streaming_bytes(p->rows, p->vocab), stream);
+    if (e != cudaSuccess) return int(e);
+  }
+  // streaming path: chunk records -> combine -> cluster kernel only for the rows the combine could not cover
+  ChunkArgs c{p->logits, p->logits_stride, p->vocab, 0, chunks, a.temperature, records, flat ? status : nullptr};
+  e = launch_chunks(c, p->rows, stream);
   if (e != cudaSuccess) return int(e);
   CombineArgs m{records, p->rows, 1, chunks, p->vocab, a.temperature, p->top_p, p->top_k, p->seeds, p->steps, p->slot,
-                p->purpose, p->tokens, status, nullptr};
+                p->purpose, p->tokens, status, nullptr, flat ? 1 : 0};
   e = launch_combine(m, false, stream);
   if (e != cudaSuccess) return int(e);
   a.status = status;

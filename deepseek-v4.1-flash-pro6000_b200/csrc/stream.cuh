@@ -40,6 +40,7 @@ __global__ void __launch_bounds__(kChunkThreads, 4) chunk_kernel(ChunkArgs a) {
   __shared__ ChunkSmem s;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int row = blockIdx.x / a.chunks, chunk = blockIdx.x % a.chunks;
+  if (a.only_uncovered && a.only_uncovered[row] != kNotCovered) return;  // the same in every thread
   const int begin = min(a.vocab_local, chunk * kChunkIds);
   const int len = min(a.vocab_local, begin + kChunkIds) - begin;
   ChunkRecord *out = a.out + size_t(row) * a.chunks + chunk;
@@ -286,6 +287,7 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineArgs a)
   extern __shared__ __align__(16) unsigned char combine_raw[];
   CombineSmem &s = *reinterpret_cast<CombineSmem *>(combine_raw);
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (a.only_uncovered && a.status[row] != kNotCovered) return;  // the same in every thread
   const int nrec = a.groups * a.per_group;
   const double t = a.temperature;
   auto rec = [&](int r) -> const ChunkRecord & {

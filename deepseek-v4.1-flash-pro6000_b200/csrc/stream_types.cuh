@@ -46,6 +46,7 @@ struct ChunkArgs {
   int vocab_local, id_offset, chunks;  // chunks per row (>= ceil(vocab_local/kChunkIds); extra chunks are empty)
   double temperature;
   ChunkRecord *out;  // [rows][chunks]
+  const int32_t *only_uncovered;  // if set: only rows whose status word there is -8 are processed
 };
 
 enum CombineMode { kCombineDraw = 0, kCombineStats = 1 };
@@ -59,6 +60,7 @@ struct CombineArgs {
   uint32_t slot, purpose;
   int32_t *tokens, *status;
   RowStats *stats;
+  int only_uncovered;  // only rows whose status word is -8 are processed (the others already have their answer)
 };
 
 

@@ -1,0 +1,104 @@
+"""GPU parity of the sampler's batch path for wide nuclei (csrc/flat.cu) against the CPU oracle: flat rows are answered
+by it (checked in its scratch records), rows it does not fit fall through to the other paths, and every token equals
+the reference rule's."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import __graft_entry__ as entry
+
+pytestmark = pytest.mark.gpu
+V = 129280
+
+
+@pytest.fixture(scope="module")
+def pkg():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    entry.build()
+    return entry.load_package()
+
+
+def u64(a):
+    return torch.from_numpy(np.asarray(a, np.uint64).view(np.int64)).cuda()
+
+
+def sample(pkg, x, t, top, seeds, steps, **kw):
+    rows, vocab = x.shape
+    scratch = torch.zeros(pkg.sample_scratch_bytes(rows, vocab), dtype=torch.uint8, device="cuda")
+    tok, st = pkg.sample_logits(x, t, top, u64(seeds), u64(steps), scratch=scratch, **kw)
+    torch.cuda.synchronize()
+    return tok.cpu().numpy(), st.cpu().numpy(), scratch
+
+
+def answered_by_batch_path(pkg, scratch, rows, vocab):
+    """`applicable` word of the per-row records (layout of launch_flat: zeroed histograms and list counters first, then
+    the window lists and the sub-region sums, then the records)."""
+    lib = pkg.lib()
+    lib.ds41_b200_shard_chunks.restype = C.c_int
+    chunks = lib.ds41_b200_shard_chunks(vocab)
+    streaming = rows * chunks * 544 + ((rows * 4 + 15) & ~15)
+    info = streaming + rows * (1024 * 8 + 1024 * 4 + 16 + 1024 * 8 + 128 * 8 + 128 * 8)
+    rec = scratch[info: info + rows * 32].cpu().numpy().view(np.int32).reshape(rows, 8)
+    return rec[:, 3] == 1
+
+
+@pytest.mark.parametrize("t,top", [(0.6, 0.95), (1.0, 0.95), (0.6, 0.5), (1.3, 0.99), (0.25, 0.9)])
+def test_flat_rows_match_oracle(pkg, oracle, t, top):
+    rows = 96
+    x = oracle.gen_normal(11, int(t * 100), (rows, V), 1.28)
+    seeds, steps = np.arange(rows) * 31 + 5, np.arange(rows) + 1000
+    want, wst = oracle.sample_rows(x, t, top, seeds, steps, slot=1, purpose=0, threads=8)
+    tok, st, scratch = sample(pkg, torch.from_numpy(x).cuda(), t, top, seeds, steps, slot=1)
+    assert (st == 0).all(), st
+    assert (tok == want).all()
+    used = answered_by_batch_path(pkg, scratch, rows, V)
+    # T=0.25 sharpens N(0,1.28^2) into a nucleus of a few hundred ids: the other paths' case
+    assert used.all() if t >= 0.6 else True
+
+
+def test_mixed_batch_falls_through_per_row(pkg, oracle):
+    """Flat rows, peaked rows (nucleus of a few ids) and rows with one towering logit in one batch."""
+    rows = 80
+    x = oracle.gen_normal(12, 0, (rows, V), 1.28)
+    x[1::4] = oracle.gen_logits(77, rows // 4, V)          # Zipf + Gaussian: peaked
+    x[2::8, 777] = 40.0                                     # one id holds all the mass: nucleus of one
+    seeds, steps = np.arange(rows) + 3, np.arange(rows) * 7
+    want, wst = oracle.sample_rows(x, 0.7, 0.9, seeds, steps, threads=8)
+    tok, st, scratch = sample(pkg, torch.from_numpy(x).cuda(), 0.7, 0.9, seeds, steps)
+    assert (st >= 0).all() and (tok == want).all(), (tok, want, st)
+    used = answered_by_batch_path(pkg, scratch, rows, V)
+    flat_rows = np.ones(rows, bool); flat_rows[1::4] = False; flat_rows[2::8] = False
+    assert used[flat_rows].all() and not used[~flat_rows].any()
+
+
+def test_nonfinite_rows_and_ragged_stride(pkg, oracle):
+    rows, vocab, stride = 64, 40001, 40004
+    buf = np.zeros((rows, stride), np.float32)
+    buf[:, :vocab] = oracle.gen_normal(13, 0, (rows, vocab), 1.0)
+    bad = [3, 17, 40]
+    buf[3, 5] = np.nan; buf[17, vocab - 1] = np.inf; buf[40, 20000] = -np.inf
+    seeds, steps = np.arange(rows), np.arange(rows) + 9
+    good = np.setdiff1d(np.arange(rows), bad)
+    want, _ = oracle.sample_rows(buf[good, :vocab].copy(), 0.8, 0.95, seeds[good], steps[good], threads=8)
+    x = torch.from_numpy(buf).cuda()[:, :vocab]
+    assert x.stride(0) == stride
+    tok, st, scratch = sample(pkg, x, 0.8, 0.95, seeds, steps)
+    assert (st[bad] == -1).all() and (tok[bad] == -1).all()
+    assert (st[good] == 0).all() and (tok[good] == want).all()
+    assert answered_by_batch_path(pkg, scratch, rows, vocab)[good].all()
+
+
+def test_same_tokens_as_cluster_kernel_at_1024_rows(pkg):
+    """Size-independent property at the bench's batch: both device paths certify and agree on every row."""
+    rows = 1024
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = 1.28 * torch.randn(rows, V, device="cuda", generator=g)
+    seeds, steps = np.arange(rows) + 17, np.full(rows, 4)
+    tok, st, scratch = sample(pkg, x, 0.6, 0.95, seeds, steps)
+    ref, rst = pkg.sample_logits(x, 0.6, 0.95, u64(seeds), u64(steps), scratch=None)
+    torch.cuda.synchronize()
+    assert (st == 0).all() and (rst.cpu().numpy() == 0).all()
+    assert (tok == ref.cpu().numpy()).all()
+    assert answered_by_batch_path(pkg, scratch, rows, V).all()
