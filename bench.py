@@ -36,10 +36,8 @@ NCU_TRAFFIC = {
     # head_fp8_kernel<64,1>, cfg2_b64: 531.43 MB read + 35.58 MB written (profiles/head_fp8_kernel_cfg2_b64.md)
     ("cfg2_b64", "head_fp8_kernel"): 567.0e6,
     # row_kernel<0>, cfg2_b64: 33.19 MB read + 256 B written (profiles/row_kernel_cfg2_b64.md)
-    ("cfg2_b64", "row_kernel"): 33.19e6,
-    # cfg5_b1024 is too large to capture with --set full under the capture-size rule; the row kernel's traffic grows in
-    # proportion to the rows (each row's logits are read once), so the cfg2_b64 capture is scaled by 1024 / 64
-    ("cfg5_b1024", "row_kernel"): 33.19e6 * 16,
+    ("cfg2_b1", "sampler"): 33.19e6 / 64,
+    # batch path of the sampler (flat_* kernels): see profiles/sampler_flat_*.md
 }
 
 
@@ -157,6 +155,10 @@ class HeadSample:
         self.status = torch.empty(batch, dtype=torch.int32, device=device)
         self.tokens_host = torch.empty(batch, dtype=torch.int32).pin_memory()
         self.flag = torch.zeros(1, dtype=torch.int32, device=device)
+        # sampler scratch: with it, batches of 64 rows or more go through the batch path for wide nuclei first
+        # (smaller batches of these flat logits go to the cluster kernel directly: the streaming path, which scratch
+        # would also enable, only covers peaked distributions)
+        self.scratch = torch.empty(pkg.sample_scratch_bytes(batch, VOCAB), dtype=torch.uint8, device=device) if batch >= 64 else None
         self.units = batch
         self.launches_per_step = 3
         self.h2d, self.d2h = batch * HIDDEN * 2, batch * 4
@@ -166,7 +168,9 @@ class HeadSample:
         self.kernels = {
             "head_fp8_kernel": {"bound": "hbm" if batch <= 128 else "tensor", "bytes": head_bytes,
                                 "flops": 2.0 * batch * self.vn * HIDDEN},
-            "row_kernel": {"bound": "hbm", "bytes": my_rows * VOCAB * 4 + my_rows * 24, "flops": 0.0},
+            # the sampler call: flat_* kernels (batch >= 64) or row_kernel (smaller batches); one read of the logits
+            # is the algorithmic minimum
+            "sampler": {"bound": "hbm", "bytes": my_rows * VOCAB * 4 + my_rows * 24, "flops": 0.0},
         }
         self.graph = None
         self.sharded = None
@@ -189,7 +193,7 @@ class HeadSample:
                 ev[1].record()
                 exch.writers_done()
                 ev[2].record()
-                exch.sample_mine(self.t, self.top_p, self.seeds, self.steps, scratch=None)
+                exch.sample_mine(self.t, self.top_p, self.seeds, self.steps)
                 ev[3].record()
                 exch.publish(self.tokens, self.status)
                 return
@@ -206,7 +210,7 @@ class HeadSample:
             ev[1].record()
             ev[2].record()
         pkg.sample_logits(self.logits, self.t, self.top_p, self.seeds, self.steps, tokens=self.tokens,
-                          status=self.status, scratch=None)  # flat logits (random head): cluster kernel directly
+                          status=self.status, scratch=self.scratch)
         if ev:
             ev[3].record()
 

@@ -144,23 +144,27 @@ __device__ __forceinline__ FlatBins make_bins(const FlatPartial &e, double t) {
   return b;
 }
 
+// Fixed-point scale of the histogram masses: an id of bin k adds round(kQ * w / 2^-(k*step)), a number in
+// (0.97 kQ, kQ]; a quarter row holds at most 32768 ids, so a 32-bit shared-memory word cannot wrap (32768 * 2^17 =
+// 2^32 is excluded by capping the addend at kQ - 1), and one integer atomic per id accumulates exactly.
+constexpr float kQ = 131072.f;
+constexpr double kQInv = 1.0 / 131072.0;
+
 __global__ void __launch_bounds__(kFT) flat_hist_kernel(FlatArgs a) {
-  __shared__ unsigned count[kFlatBins], qmass[kFlatBins];
+  __shared__ unsigned qmass[kFlatBins];
   const int row = blockIdx.x / kFlatChunks, chunk = blockIdx.x % kFlatChunks;
   const FlatPartial ext = row_extremes(a, row);
   if (ext.flags || !(ext.min < ext.max)) return;  // the window kernel reports the row
   const FlatBins b = make_bins(ext, a.t);
-  for (int j = threadIdx.x; j < kFlatBins; j += kFT) { count[j] = 0u; qmass[j] = 0u; }
+  for (int j = threadIdx.x; j < kFlatBins; j += kFT) qmass[j] = 0u;
   __syncthreads();
   int begin, end;
   quarter(a, chunk, &begin, &end);
   const float *x = a.logits + size_t(row) * a.stride;
-  // an id of bin k adds round(2^20 * w / 2^-(k*step)), a number in (2^19, 2^20]: integer atomics accumulate it exactly
   auto take = [&](float y) {
     const float d = b.m - y;
     const int k = min(kFlatBins - 1, int(d * b.inv_w));
-    atomicAdd(&count[k], 1u);
-    atomicAdd(&qmass[k], __float2uint_rn(1048576.f * ex2_approx(fmaf(float(k), b.step, -(d * b.c32)))));
+    atomicAdd(&qmass[k], min(131071u, __float2uint_rn(kQ * ex2_approx(fmaf(float(k), b.step, -(d * b.c32))))));
   };
   const int vec_end = begin + ((end - begin) & ~3);
   for (int i = begin + 4 * threadIdx.x; i < vec_end; i += 4 * kFT) {
@@ -169,16 +173,10 @@ __global__ void __launch_bounds__(kFT) flat_hist_kernel(FlatArgs a) {
   }
   for (int i = vec_end + threadIdx.x; i < end; i += kFT) take(__ldg(x + i));
   __syncthreads();
-  bool crowded = false;  // 4096 or more ids of this quarter row in one bin: the 32-bit mass may have wrapped
   for (int j = threadIdx.x; j < kFlatBins; j += kFT) {
-    const unsigned n = count[j];
-    if (n) {
-      atomicAdd(&a.s.hcount[size_t(row) * kFlatBins + j], n);
-      atomicAdd(&a.s.hmass[size_t(row) * kFlatBins + j], (unsigned long long)qmass[j]);
-      crowded |= n >= 4096u;
-    }
+    const unsigned q = qmass[j];
+    if (q) atomicAdd(&a.s.hmass[size_t(row) * kFlatBins + j], (unsigned long long)q);
   }
-  if (crowded) atomicOr(&a.s.lcount[row * 4 + 1], 1);
 }
 
 __global__ void __launch_bounds__(kFT) flat_window_kernel(FlatArgs a) {
@@ -198,19 +196,26 @@ __global__ void __launch_bounds__(kFT) flat_window_kernel(FlatArgs a) {
     return;
   }
   const FlatBins b = make_bins(ext, a.t);
-  int cnt[2] = {0, 0};
+  // ids of a bin, bracketed from its fixed-point mass (every id adds between 0.97 kQ and kQ): enough to tell a wide
+  // nucleus from a small one and whether the window fits the list; the exact counts come from the FP64 pass
+  int cnt_lo[2] = {0, 0}, cnt_hi[2] = {0, 0};
   double lo[2] = {0, 0}, hi[2] = {0, 0};
   if (ext.min < ext.max) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       const int k = 2 * threadIdx.x + i;
-      cnt[i] = int(a.s.hcount[size_t(row) * kFlatBins + k]);
       const unsigned long long q = a.s.hmass[size_t(row) * kFlatBins + k];
-      // error of the measured mass of a bin: see row_wide.cuh (the arithmetic per id is the same)
+      // Error of the measured mass of a bin, per id: the FP32 argument carries three roundings relative to
+      // |x| <= (k+1)*step plus one of the product k*step (together < 2.8 |x| * 2^-24 in the weight; 5.6 allowed),
+      // ex2.approx is within 2^-22, the product by kQ within 2^-24, the rounding to an integer (and the cap at
+      // kQ - 1) within 2^-17 of a value near kQ = 128 * 2^-24; the edge weight below is an FP64 exp2 of the same
+      // FP32 product.  Integer accumulation adds nothing.
       const double x_far = (double(k) + 1.0) * double(b.step) * 1.0001;
-      const double e = (5.6 * x_far + 41.0) * 5.9604644775390625e-8;
-      const double mass = double(q) * 9.5367431640625e-7 * exp2(-double(float(k) * b.step));
+      const double e = (5.6 * x_far + 4.0 + 1.0 + 160.0 + 4.0) * 5.9604644775390625e-8;
+      const double mass = double(q) * kQInv * exp2(-double(float(k) * b.step));
       lo[i] = mass * (1.0 - e); hi[i] = mass * (1.0 + e);
+      cnt_lo[i] = int(q >> 17);                                   // every id adds at most kQ
+      cnt_hi[i] = int((double(q) * kQInv) / 0.97) + (q ? 1 : 0);  // and at least 0.97 kQ (bin width << 0.04 in exponent)
     }
   }
   const double lo0 = flat_prefix2(red, lo[0], lo[1]), hi0 = flat_prefix2(red, hi[0], hi[1]);
@@ -229,15 +234,15 @@ __global__ void __launch_bounds__(kFT) flat_window_kernel(FlatArgs a) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       const int k = 2 * threadIdx.x + i;
-      if (k <= w1) { through += cnt[i]; if (k >= w0) inside += cnt[i]; }
+      if (k <= w1) { through += cnt_lo[i]; if (k >= w0) inside += cnt_hi[i]; }
     }
   }
   through = flat_sum(red, through);
   inside = flat_sum(red, inside);
-  const bool crowded = a.s.lcount[row * 4 + 1] != 0;
   // this path's case: a window exists, the nucleus is wide (a small one is the other paths' case), the window fits
-  // the list, no mass wrapped
-  const bool ok = found && through > kFlatMinNucleus && inside <= kFlatList && !crowded;
+  // the list, and the bins are narrow enough for the count bracket above (step <= 0.04: any row whose range times
+  // 1.44/T is below 41)
+  const bool ok = found && through > kFlatMinNucleus && inside <= kFlatList && b.step <= 0.04f;
   if (threadIdx.x == 0) {
     info.applicable = ok ? 1 : 0; info.w0 = w0; info.w1 = w1;
     a.s.info[row] = info;
@@ -262,31 +267,50 @@ __global__ void __launch_bounds__(kFT) flat_mass_kernel(FlatArgs a) {
     const int base = sub * kFlatSub;
     double z = 0, sure_mass = 0;
     int sure_count = 0;
-    for (int it = 0; it < kFlatSub; it += 32) {
-      const int id = base + it + lane;
-      bool inside = false;
-      float y = 0.f;
-      if (id < a.vocab) {
-        y = __ldg(x + id);
-        const double e = exp_nonpos((double(y) - m64) * inv_t);
-        z += e;
-        // bin(y) < w0 and bin(y) <= w1 without forming the bin: int(v) < k is v < k for v >= 0
-        const float v = (b.m - y) * b.inv_w;
-        const bool sure = v < edge0;
-        if (sure) { sure_mass += e; ++sure_count; }
-        inside = !sure && v < edge1;
+    // the whole sub-region goes to registers first (eight 16-byte loads per lane in flight): the pass is bound by
+    // memory latency otherwise
+    float4 buf[kFlatSub / 128];
+#pragma unroll
+    for (int j = 0; j < kFlatSub / 128; ++j) {
+      const int id = base + (j * 32 + lane) * 4;
+      if (id + 3 < a.vocab) {
+        buf[j] = __ldg(reinterpret_cast<const float4 *>(x + id));
+      } else {
+        buf[j].x = id < a.vocab ? __ldg(x + id) : 0.f;
+        buf[j].y = id + 1 < a.vocab ? __ldg(x + id + 1) : 0.f;
+        buf[j].z = id + 2 < a.vocab ? __ldg(x + id + 2) : 0.f;
+        buf[j].w = 0.f;
       }
-      const unsigned ballot = __ballot_sync(0xffffffffu, inside);
-      if (ballot) {
-        int slot0 = 0;
-        if (lane == 0) slot0 = atomicAdd(&a.s.lcount[row * 4], __popc(ballot));
-        slot0 = __shfl_sync(0xffffffffu, slot0, 0);
-        if (inside) {
-          const int slot = slot0 + __popc(ballot & ((1u << lane) - 1u));
-          // ascending 64-bit key = (logit descending, id ascending); +0 and -0 compare equal as logits: both map to +0
-          const float yy = y == 0.f ? 0.f : y;
-          const uint32_t bits = __float_as_uint(yy), ordered = bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u);
-          if (slot < kFlatList) a.s.lkeys[size_t(row) * kFlatList + slot] = (unsigned long long)(~ordered) << 32 | uint32_t(id);
+    }
+#pragma unroll
+    for (int j = 0; j < kFlatSub / 128; ++j) {
+      const float ys4[4] = {buf[j].x, buf[j].y, buf[j].z, buf[j].w};
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const int id = base + (j * 32 + lane) * 4 + q4;
+        const float y = ys4[q4];
+        bool inside = false;
+        if (id < a.vocab) {
+          const double e = exp_nonpos((double(y) - m64) * inv_t);
+          z += e;
+          // bin(y) < w0 and bin(y) <= w1 without forming the bin: int(v) < k is v < k for v >= 0
+          const float v = (b.m - y) * b.inv_w;
+          const bool sure = v < edge0;
+          if (sure) { sure_mass += e; ++sure_count; }
+          inside = !sure && v < edge1;
+        }
+        const unsigned ballot = __ballot_sync(0xffffffffu, inside);
+        if (ballot) {
+          int slot0 = 0;
+          if (lane == 0) slot0 = atomicAdd(&a.s.lcount[row * 4], __popc(ballot));
+          slot0 = __shfl_sync(0xffffffffu, slot0, 0);
+          if (inside) {
+            const int slot = slot0 + __popc(ballot & ((1u << lane) - 1u));
+            // ascending 64-bit key = (logit descending, id ascending); +0 and -0 compare equal as logits: both map to +0
+            const float yy = y == 0.f ? 0.f : y;
+            const uint32_t bits = __float_as_uint(yy), ordered = bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u);
+            if (slot < kFlatList) a.s.lkeys[size_t(row) * kFlatList + slot] = (unsigned long long)(~ordered) << 32 | uint32_t(id);
+          }
         }
       }
     }
@@ -510,7 +534,7 @@ cudaError_t launch_flat(FlatArgs a, void *scratch, cudaStream_t stream) {
   unsigned char *p = static_cast<unsigned char *>(scratch);
   const size_t rows = size_t(a.rows);
   a.s.hmass = reinterpret_cast<unsigned long long *>(p); p += rows * kFlatBins * sizeof(unsigned long long);
-  a.s.hcount = reinterpret_cast<unsigned *>(p); p += rows * kFlatBins * sizeof(unsigned);
+  a.s.hcount = reinterpret_cast<unsigned *>(p); p += rows * kFlatBins * sizeof(unsigned);  // (kept for layout; unused)
   a.s.lcount = reinterpret_cast<int *>(p); p += rows * 4 * sizeof(int);
   const size_t zeroed = size_t(p - static_cast<unsigned char *>(scratch));
   a.s.lkeys = reinterpret_cast<unsigned long long *>(p); p += rows * kFlatList * sizeof(unsigned long long);

@@ -200,6 +200,8 @@ class RowExchange:
         self.full.zero_()
         self.word = torch.zeros(1, dtype=torch.int32, device=device)
         self.packed = torch.full((2, self.rows_per_owner), -1, dtype=torch.int32, device=device)
+        self.scratch = torch.empty(max(16, pkg.sample_scratch_bytes(max(1, self.my_rows), vocab)), dtype=torch.uint8,
+                                   device=device)
         self.everyone = torch.empty((self.world, 2, self.rows_per_owner), dtype=torch.int32, device=device)
         if self.world > 1:
             dist.barrier(group=group)  # every buffer exists and is mapped before anyone writes
@@ -223,6 +225,7 @@ class RowExchange:
 
     def sample_mine(self, temperature, top_p, seeds, steps, slot=0, purpose=0, **kw):
         n = self.my_rows
+        kw.setdefault("scratch", self.scratch)
         if n:
             sl = slice(self.row0, self.row0 + n)
             self.pkg.sample_logits(self.full[:n], temperature, top_p, seeds[sl], steps[sl], slot=slot, purpose=purpose,
@@ -275,7 +278,7 @@ class ShardedDecodeTail:
             ex = self.exchange
             ex.head_scatter(a, a_scale, w, w_scale, self.v0, error_flag)
             ex.writers_done()
-            ex.sample_mine(self.t, self.top_p, seeds, steps, slot, purpose, scratch=None)
+            ex.sample_mine(self.t, self.top_p, seeds, steps, slot, purpose)
             ex.publish(tokens, status)
             self.rows_mode_left -= 1
             self.steps_rows += 1
