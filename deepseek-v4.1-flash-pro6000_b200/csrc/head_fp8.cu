@@ -29,9 +29,8 @@
 namespace ds41 {
 namespace {
 
-constexpr int kTileN = 128;   // vocabulary rows per tile (UMMA N; the UMMA M dimension, 128, takes the batch rows)
+constexpr int kTmemColumns = 512;  // all of an SM's tensor memory: 4 accumulators of 128 columns or 2 of 256
 constexpr int kTileK = 128;   // K elements per block = one 128-byte swizzle row of e4m3
-constexpr int kAccBufs = 4;   // TMEM accumulators in flight (K blocks between the MMA issuer and the epilogue)
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -94,7 +93,7 @@ constexpr uint64_t kDescFixed = (uint64_t(1) << 16)              // leading byte
 __device__ __forceinline__ uint64_t umma_desc16(uint32_t addr16) { return kDescFixed | uint64_t(addr16); }
 // Instruction descriptor for kind::f8f6f4, E4M3 x E4M3 -> F32, both operands K-major, M=128, N=n_cols.
 __host__ __device__ constexpr uint32_t umma_idesc(int n_cols) {
-  return (1u << 4) | (uint32_t(n_cols >> 3) << 17) | (uint32_t(kTileN >> 4) << 24);
+  return (1u << 4) | (uint32_t(n_cols >> 3) << 17) | (uint32_t(128 >> 4) << 24);
 }
 template <bool kAccumulate>
 __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
@@ -127,9 +126,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
 }
 
-template <int kRows>
+// kRows batch rows x kVocab vocabulary ids per output tile (kVocab = UMMA N: 128, or 256 to halve the activation
+// traffic per output element when the batch is large and the kernel is bound by L2 -> shared-memory copies)
+template <int kRows, int kVocab>
 struct HeadSmem {
-  static constexpr int kStageBytes = kTileN * kTileK + kRows * kTileK;
+  static constexpr int kAccBufs = kTmemColumns / kVocab;
+  static constexpr int kStageBytes = kVocab * kTileK + kRows * kTileK;
   // the MMA reads 128 activation rows from every stage; with kRows < 128 the rows beyond the tile belong to the next
   // stage (or to the pad after the last one) and only feed TMEM lanes nobody reads
   static constexpr int kPadBytes = (128 - kRows) * kTileK;
@@ -164,21 +166,23 @@ struct HeadArgs {
   int group;             // K blocks per stage: every row of a weight tile is fetched as group*128 contiguous bytes
 };
 
-template <int kRows>
+template <int kRows, int kVocab>
 __global__ void __launch_bounds__(kHeadThreads, 1)
 head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, HeadArgs p) {
-  constexpr int kStageBytes = HeadSmem<kRows>::kStageBytes;
-  constexpr int kMaxStages = HeadSmem<kRows>::kMaxStages;
+  using Smem = HeadSmem<kRows, kVocab>;
+  constexpr int kTileN = kVocab, kAccBufs = Smem::kAccBufs;
+  constexpr int kStageBytes = Smem::kStageBytes;
+  constexpr int kMaxStages = Smem::kMaxStages;
   const int kStages = p.stages, group = p.group;
   const int stage_bytes = kStageBytes * group, w_bytes = kTileN * kTileK * group;  // [W g0..][A g0..]
-  constexpr uint32_t kTmemCols = kAccBufs * kTileN;  // 512: four accumulators of 128 columns
+  constexpr uint32_t kTmemCols = kTmemColumns;
   constexpr int kQuads = (kRows + 31) / 32;          // lane quadrants that hold real batch rows
-  constexpr int kGroups = 4, kMyCols = kTileN / kGroups;  // 32-column groups: warp (quadrant q, group g)
+  constexpr int kGroups = 4, kMyCols = kTileN / kGroups;  // 32- or 64-column groups: warp (quadrant q, group g)
   constexpr int kEpiActive = 32 * kQuads * kGroups;  // epilogue threads that take part
   extern __shared__ __align__(1024) unsigned char smem[];
   // carve: [stages][W tile 16 KB | A tile kRows*128 B], pad, then the activation-scale table, then barriers
   unsigned char *tiles = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~uintptr_t(1023));
-  float *sa = reinterpret_cast<float *>(tiles + size_t(kStages) * stage_bytes + HeadSmem<kRows>::kPadBytes);  // [K/128][kRows]
+  float *sa = reinterpret_cast<float *>(tiles + size_t(kStages) * stage_bytes + Smem::kPadBytes);  // [K/128][kRows]
   const int kblocks = p.K / kTileK;
   uint64_t *bars = reinterpret_cast<uint64_t *>(sa + size_t(kblocks) * kRows);
   uint64_t *full = bars, *empty = bars + kMaxStages, *acc_full = bars + 2 * kMaxStages, *acc_empty = acc_full + kAccBufs;
@@ -273,7 +277,9 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiActive) : "memory");
         table_bt = bt;
       }
-      const float *wsc = p.w_scale + size_t(nt) * kblocks;
+      // fp32 scale of the 128-row weight block this warp's columns belong to (a 256-wide tile spans two blocks)
+      const int w_block = min((nt * kTileN + group * kMyCols) / 128, (p.N + 127) / 128 - 1);
+      const float *wsc = p.w_scale + size_t(w_block) * kblocks;
       float sum[kMyCols];
 #pragma unroll
       for (int c = 0; c < kMyCols; ++c) sum[c] = 0.f;
@@ -282,27 +288,47 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         alive = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], acc_phase, ab));
         if (!alive) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        uint32_t r[32];
-        tmem_ld32(lane_base + acc * kTileN, r);
         const float scale = sa[kb * kRows + (row < kRows ? row : 0)] * w_next;
         if (kb + 1 < kblocks) w_next = __ldg(wsc + kb + 1);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        // the values are in registers: the accumulator can be refilled while they are scaled and added
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[acc]);
-        if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1; }
+        if constexpr (kMyCols == 32) {
+          uint32_t r[32];
+          tmem_ld32(lane_base + acc * kTileN, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          // the values are in registers: the accumulator can be refilled while they are scaled and added
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[acc]);
 #pragma unroll
-        for (int c = 0; c < kMyCols; ++c) sum[c] = fmaf(__uint_as_float(r[c]), scale, sum[c]);
+          for (int c = 0; c < 32; ++c) sum[c] = fmaf(__uint_as_float(r[c]), scale, sum[c]);
+        } else {
+          // 64 columns per thread: four 16-column loads, one in flight at a time (the register budget of 576 threads)
+#pragma unroll
+          for (int c0 = 0; c0 < kMyCols; c0 += 16) {
+            uint32_t r[32];
+            tmem_ld16(lane_base + acc * kTileN + c0, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (c0 + 16 == kMyCols) {
+              asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&acc_empty[acc]);
+            }
+#pragma unroll
+            for (int c = 0; c < 16; ++c) sum[c0 + c] = fmaf(__uint_as_float(r[c]), scale, sum[c0 + c]);
+          }
+        }
+        if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1; }
       }
       // Output.  Lane l holds row l of the warp's 32 x 32 block.  Written as it is, one store instruction would touch
       // 32 rows with 16 bytes each; an 8 x 8 transpose of the 16-byte column groups across the lanes that share
       // l % 4 (butterflies at lane distances 4, 8, 16) turns that into 4 rows with 128 contiguous bytes each, which is
       // what a peer GPU's memory wants to be written with (and the local L2 as well).
       if (alive) {
+#pragma unroll
+       for (int half = 0; half < kMyCols / 32; ++half) {
         float4 x[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) x[c] = make_float4(sum[4 * c], sum[4 * c + 1], sum[4 * c + 2], sum[4 * c + 3]);
+        for (int c = 0; c < 8; ++c)
+          x[c] = make_float4(sum[32 * half + 4 * c], sum[32 * half + 4 * c + 1], sum[32 * half + 4 * c + 2], sum[32 * half + 4 * c + 3]);
 #pragma unroll
         for (int s3 = 0; s3 < 3; ++s3) {
           const int dist = 4 << s3;
@@ -321,7 +347,7 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           }
         }
         // now x[a] = columns [4*(lane/4), +4) of block row 4*a + lane%4
-        const int n = nt * kTileN + group * kMyCols + 4 * (lane >> 2);
+        const int n = nt * kTileN + group * kMyCols + 32 * half + 4 * (lane >> 2);
 #pragma unroll
         for (int a8 = 0; a8 < 8; ++a8) {
           const int r = quad * 32 + 4 * a8 + (lane & 3), m = bt * kRows + r;
@@ -342,6 +368,7 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
               if (n + k < p.N) dst[k] = v[k];
           }
         }
+       }
       }
     }
   }
@@ -409,11 +436,12 @@ bool make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, 
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int kRows>
+template <int kRows, int kVocab>
 cudaError_t launch_head(const CUtensorMap &mw, const CUtensorMap &ma, const HeadArgs &p, int sms, cudaStream_t stream) {
-  const int stages = HeadSmem<kRows>::stages(p.K / kTileK, p.group);
+  using Smem = HeadSmem<kRows, kVocab>;
+  const int stages = Smem::stages(p.K / kTileK, p.group);
   if (stages < 2) return cudaErrorInvalidValue;
-  const size_t smem = HeadSmem<kRows>::fixed_bytes(p.K / kTileK) + size_t(stages) * HeadSmem<kRows>::kStageBytes * p.group;
+  const size_t smem = Smem::fixed_bytes(p.K / kTileK) + size_t(stages) * Smem::kStageBytes * p.group;
   HeadArgs q = p;
   q.stages = stages;
   static thread_local int configured = -1;
@@ -421,16 +449,16 @@ cudaError_t launch_head(const CUtensorMap &mw, const CUtensorMap &ma, const Head
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (configured != dev) {
-    e = cudaFuncSetAttribute(head_fp8_kernel<kRows>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    e = cudaFuncSetAttribute(head_fp8_kernel<kRows, kVocab>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     configured = dev;
   }
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
   const int b_tiles = (p.M + kRows - 1) / kRows;
-  const int tiles = ((p.N + kTileN - 1) / kTileN) * b_tiles;
+  const int tiles = ((p.N + kVocab - 1) / kVocab) * b_tiles;
   int grid = tiles < sms ? tiles : sms;
   if (b_tiles <= grid) grid -= grid % b_tiles;  // every CTA then keeps one batch tile (and its scale table) for good
-  head_fp8_kernel<kRows><<<grid, kHeadThreads, smem, stream>>>(mw, ma, q);
+  head_fp8_kernel<kRows, kVocab><<<grid, kHeadThreads, smem, stream>>>(mw, ma, q);
   return cudaGetLastError();
 }
 
@@ -496,12 +524,16 @@ int run_head(const void *a_e4m3, const float *a_scale, const void *w_e4m3, const
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (e != cudaSuccess) return int(e);
   const int cols = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+  // Vocabulary tile: 256 wide once the batch spans several tiles (then the kernel is bound by L2 -> shared-memory
+  // copies and a wider tile re-reads the activations half as often), else 128.
+  const int vocab_tile = (M > 128 && N >= 256) ? 256 : 128;
   // K blocks per stage: the largest of 4, 2, 1 that divides K/128 and still leaves a ring of at least 2 stages
   // (measured: longer contiguous runs per weight row beat a deeper ring of shorter ones)
   const int kblocks = K / kTileK;
   auto ring = [&](int g) {
-    return cols == 16 ? HeadSmem<16>::stages(kblocks, g) : cols == 32 ? HeadSmem<32>::stages(kblocks, g)
-         : cols == 64 ? HeadSmem<64>::stages(kblocks, g) : HeadSmem<128>::stages(kblocks, g);
+    return vocab_tile == 256 ? HeadSmem<128, 256>::stages(kblocks, g)
+         : cols == 16 ? HeadSmem<16, 128>::stages(kblocks, g) : cols == 32 ? HeadSmem<32, 128>::stages(kblocks, g)
+         : cols == 64 ? HeadSmem<64, 128>::stages(kblocks, g) : HeadSmem<128, 128>::stages(kblocks, g);
   };
   int group = 1;
   for (int g = 4; g > 1; g >>= 1)
@@ -512,14 +544,15 @@ int run_head(const void *a_e4m3, const float *a_scale, const void *w_e4m3, const
   }
   p.group = group;
   CUtensorMap mw, ma;
-  if (!make_map(&mw, w_e4m3, uint64_t(N), uint64_t(K), kTileN, uint32_t(group)) ||
+  if (!make_map(&mw, w_e4m3, uint64_t(N), uint64_t(K), uint32_t(vocab_tile), uint32_t(group)) ||
       !make_map(&ma, a_e4m3, uint64_t(M), uint64_t(K), uint32_t(cols), uint32_t(group)))
     return invalid("cuTensorMapEncodeTiled failed");
+  if (vocab_tile == 256) return int(launch_head<128, 256>(mw, ma, p, sms, stream));
   switch (cols) {
-    case 16: e = launch_head<16>(mw, ma, p, sms, stream); break;
-    case 32: e = launch_head<32>(mw, ma, p, sms, stream); break;
-    case 64: e = launch_head<64>(mw, ma, p, sms, stream); break;
-    default: e = launch_head<128>(mw, ma, p, sms, stream); break;
+    case 16: e = launch_head<16, 128>(mw, ma, p, sms, stream); break;
+    case 32: e = launch_head<32, 128>(mw, ma, p, sms, stream); break;
+    case 64: e = launch_head<64, 128>(mw, ma, p, sms, stream); break;
+    default: e = launch_head<128, 128>(mw, ma, p, sms, stream); break;
   }
   return int(e);
 }
