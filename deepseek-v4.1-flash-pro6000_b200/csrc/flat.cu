@@ -250,7 +250,30 @@ __global__ void __launch_bounds__(kFT) flat_window_kernel(FlatArgs a) {
   }
 }
 
-__global__ void __launch_bounds__(kFT) flat_mass_kernel(FlatArgs a) {
+// Weight of an id BEYOND the window (it only enters the normaliser, and all such ids together hold less than
+// 1 - top_p of it) in FP32-class arithmetic: 2^-X with X = (m - y) * log2(e)/T formed in double-float (the difference
+// by TwoSum, the product with the constant split in two floats: X is good to 3 * 2^-47 relative), split X = n + f with
+// |f| <= 1/2, ex2.approx(-f) (within 2^-22) times the exact power 2^-n.  Relative error of the result below 2.7e-7
+// (test: against long double on 10^7 arguments); weights below 2^-126 come out as 0.
+struct TailExp { float m, c_hi, c_lo; };
+__device__ __forceinline__ float tail_weight(float y, const TailExp &k) {
+  const float s = __fsub_rn(k.m, y);
+  const float bb = __fsub_rn(s, k.m);
+  const float ed = __fadd_rn(__fsub_rn(k.m, __fsub_rn(s, bb)), __fsub_rn(-y, bb));  // m - y = s + ed exactly
+  const float p = __fmul_rn(s, k.c_hi);
+  const float pe = __fmaf_rn(s, k.c_hi, -p);                                        // s * c_hi = p + pe exactly
+  const float q = __fmaf_rn(s, k.c_lo, __fmaf_rn(ed, k.c_hi, pe));
+  const float n = rintf(p);
+  const float f = __fadd_rn(__fsub_rn(p, n), q);
+  const int ni = int(n);
+  return ni > 126 ? 0.f : __fmul_rn(ex2_approx(-f), __int_as_float((127 - ni) << 23));
+}
+constexpr double kTailRel = 4.5e-7;  // per-term 2.7e-7 + compensated FP32 summation 1.2e-7, rounded up
+
+__global__ void __launch_bounds__(kFT, 2) flat_mass_kernel(FlatArgs a) {
+  // per-warp queue of the ids that need an FP64 weight (before or inside the window): position in the sub-region
+  __shared__ float queue_y[kFW][256];
+  __shared__ unsigned short queue_at[kFW][256];
   const int row = blockIdx.x / kFlatChunks, chunk = blockIdx.x % kFlatChunks;
   const FlatInfo info = a.s.info[row];
   if (!info.applicable) return;
@@ -259,6 +282,8 @@ __global__ void __launch_bounds__(kFT) flat_mass_kernel(FlatArgs a) {
   const FlatBins b = make_bins(ext, a.t);
   const float edge0 = float(info.w0), edge1 = info.w1 >= kFlatBins - 1 ? CUDART_INF_F : float(info.w1 + 1);
   const double inv_t = 1.0 / a.t, m64 = double(info.max);
+  const double c64 = 1.4426950408889634074 / a.t;
+  const TailExp tail{info.max, float(c64), float(c64 - double(float(c64)))};
   const float *x = a.logits + size_t(row) * a.stride;
   constexpr int kSubsPerWarp = kFlatSubs / kFlatChunks / kFW;  // 2
 #pragma unroll 1
@@ -267,63 +292,98 @@ __global__ void __launch_bounds__(kFT) flat_mass_kernel(FlatArgs a) {
     const int base = sub * kFlatSub;
     double z = 0, sure_mass = 0;
     int sure_count = 0;
-    // the whole sub-region goes to registers first (eight 16-byte loads per lane in flight): the pass is bound by
-    // memory latency otherwise
-    float4 buf[kFlatSub / 128];
-#pragma unroll
-    for (int j = 0; j < kFlatSub / 128; ++j) {
-      const int id = base + (j * 32 + lane) * 4;
-      if (id + 3 < a.vocab) {
-        buf[j] = __ldg(reinterpret_cast<const float4 *>(x + id));
-      } else {
-        buf[j].x = id < a.vocab ? __ldg(x + id) : 0.f;
-        buf[j].y = id + 1 < a.vocab ? __ldg(x + id + 1) : 0.f;
-        buf[j].z = id + 2 < a.vocab ? __ldg(x + id + 2) : 0.f;
-        buf[j].w = 0.f;
+    float tail_sum = 0.f, tail_comp = 0.f;  // compensated FP32 sum of the lane's tail weights
+    int head = 0, count = 0;                // queue state, warp-uniform
+    // FP64 weights of up to 32 queued ids (lane i takes entry head + i)
+    auto drain = [&](int take) {
+      const bool mine = lane < take;
+      const int slot = (head + lane) & 255;
+      const float y = mine ? queue_y[warp][slot] : 0.f;
+      const int id = base + (mine ? int(queue_at[warp][slot]) : 0);
+      bool inside = false;
+      if (mine) {
+        const double e = exp_nonpos((double(y) - m64) * inv_t);
+        z += e;
+        // bin(y) < w0 without forming the bin: int(v) < k is v < k for v >= 0
+        const bool sure = (b.m - y) * b.inv_w < edge0;
+        if (sure) { sure_mass += e; ++sure_count; }
+        inside = !sure;
       }
-    }
-#pragma unroll
+      const unsigned ballot = __ballot_sync(0xffffffffu, inside);
+      if (ballot) {
+        int slot0 = 0;
+        if (lane == 0) slot0 = atomicAdd(&a.s.lcount[row * 4], __popc(ballot));
+        slot0 = __shfl_sync(0xffffffffu, slot0, 0);
+        if (inside) {
+          const int at = slot0 + __popc(ballot & ((1u << lane) - 1u));
+          // ascending 64-bit key = (logit descending, id ascending); +0 and -0 compare equal as logits: both map to +0
+          const float yy = y == 0.f ? 0.f : y;
+          const uint32_t bits = __float_as_uint(yy), ordered = bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u);
+          if (at < kFlatList) a.s.lkeys[size_t(row) * kFlatList + at] = (unsigned long long)(~ordered) << 32 | uint32_t(id);
+        }
+      }
+      head = (head + take) & 255;
+      count -= take;
+      __syncwarp();  // the drained slots may be written again
+    };
+    // 128 ids per round (one 16-byte load per lane), the next round's load in flight while this one is processed
+    auto fetch = [&](int j) {
+      const int id = base + (j * 32 + lane) * 4;
+      float4 v;
+      if (id + 3 < a.vocab) {
+        v = __ldg(reinterpret_cast<const float4 *>(x + id));
+      } else {
+        v.x = id < a.vocab ? __ldg(x + id) : 0.f;
+        v.y = id + 1 < a.vocab ? __ldg(x + id + 1) : 0.f;
+        v.z = id + 2 < a.vocab ? __ldg(x + id + 2) : 0.f;
+        v.w = 0.f;
+      }
+      return v;
+    };
+    float4 cur = fetch(0);
+#pragma unroll 1
     for (int j = 0; j < kFlatSub / 128; ++j) {
-      const float ys4[4] = {buf[j].x, buf[j].y, buf[j].z, buf[j].w};
+      const float4 nxt = j + 1 < kFlatSub / 128 ? fetch(j + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float ys4[4] = {cur.x, cur.y, cur.z, cur.w};
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
-        const int id = base + (j * 32 + lane) * 4 + q4;
+        const int at = (j * 32 + lane) * 4 + q4;
         const float y = ys4[q4];
-        bool inside = false;
-        if (id < a.vocab) {
-          const double e = exp_nonpos((double(y) - m64) * inv_t);
-          z += e;
-          // bin(y) < w0 and bin(y) <= w1 without forming the bin: int(v) < k is v < k for v >= 0
-          const float v = (b.m - y) * b.inv_w;
-          const bool sure = v < edge0;
-          if (sure) { sure_mass += e; ++sure_count; }
-          inside = !sure && v < edge1;
+        const bool valid = base + at < a.vocab;
+        // ids up to the window's far edge go to the FP64 queue, the others are tail
+        const bool near = valid && (b.m - y) * b.inv_w < edge1;
+        if (valid && !near) {
+          const float w = tail_weight(y, tail);
+          const float t1 = __fsub_rn(w, tail_comp), t2 = __fadd_rn(tail_sum, t1);
+          tail_comp = __fsub_rn(__fsub_rn(t2, tail_sum), t1);
+          tail_sum = t2;
         }
-        const unsigned ballot = __ballot_sync(0xffffffffu, inside);
-        if (ballot) {
-          int slot0 = 0;
-          if (lane == 0) slot0 = atomicAdd(&a.s.lcount[row * 4], __popc(ballot));
-          slot0 = __shfl_sync(0xffffffffu, slot0, 0);
-          if (inside) {
-            const int slot = slot0 + __popc(ballot & ((1u << lane) - 1u));
-            // ascending 64-bit key = (logit descending, id ascending); +0 and -0 compare equal as logits: both map to +0
-            const float yy = y == 0.f ? 0.f : y;
-            const uint32_t bits = __float_as_uint(yy), ordered = bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u);
-            if (slot < kFlatList) a.s.lkeys[size_t(row) * kFlatList + slot] = (unsigned long long)(~ordered) << 32 | uint32_t(id);
-          }
+        const unsigned ballot = __ballot_sync(0xffffffffu, near);
+        if (near) {
+          const int slot = (head + count + __popc(ballot & ((1u << lane) - 1u))) & 255;
+          queue_y[warp][slot] = y;
+          queue_at[warp][slot] = (unsigned short)at;
         }
+        count += __popc(ballot);
+        __syncwarp();
       }
+      while (count >= 32) drain(32);
+      cur = nxt;
     }
+    if (count > 0) drain(count);
+    double tail64 = double(tail_sum) - double(tail_comp);
 #pragma unroll
     for (int o = 16; o; o >>= 1) {
       z += __shfl_xor_sync(0xffffffffu, z, o);
       sure_mass += __shfl_xor_sync(0xffffffffu, sure_mass, o);
+      tail64 += __shfl_xor_sync(0xffffffffu, tail64, o);
     }
     sure_count = __reduce_add_sync(0xffffffffu, sure_count);
     if (lane == 0) {
-      a.s.subz[size_t(row) * kFlatSubs + sub] = z;
+      a.s.subz[size_t(row) * kFlatSubs + sub] = z + tail64;
       a.s.subsure[size_t(row) * kFlatSubs + sub] = sure_mass;
       a.s.subcnt[size_t(row) * kFlatSubs + sub] = sure_count;
+      a.s.subtail[size_t(row) * kFlatSubs + sub] = tail64;
     }
   }
 }
@@ -344,15 +404,17 @@ __global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
   const float *x = a.logits + size_t(row) * a.stride;
   const int listed = a.s.lcount[row * 4];
   // normaliser, mass and count before the window: fixed order (sub-regions across threads, then the block tree)
-  double z = 0, mass_before = 0;
+  double z = 0, mass_before = 0, tail = 0;
   int n_before = 0;
   if (tid < kFlatSubs) {
     z = a.s.subz[size_t(row) * kFlatSubs + tid];
+    tail = a.s.subtail[size_t(row) * kFlatSubs + tid];
     mass_before = a.s.subsure[size_t(row) * kFlatSubs + tid];
     n_before = a.s.subcnt[size_t(row) * kFlatSubs + tid];
     ksum[tid] = mass_before;
   }
   z = flat_sum(red, z);
+  tail = flat_sum(red, tail);
   mass_before = flat_sum(red, mass_before);
   n_before = flat_sum(red, n_before);
   bool ok = listed >= 1 && listed <= kFlatList;
@@ -410,7 +472,9 @@ __global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
   }
   const double through0 = mass_before + flat_prefix2(red, e[0], e[1]), through1 = through0 + e[1];
   const double rel = 2.0 * (double(a.vocab) + 256.0) * kU;
-  const double target_p = a.top_p * z, lo = target_p * (1.0 - rel), hi = target_p * (1.0 + rel);
+  // the ids beyond the window entered z with FP32-class weights: their share of z carries a relative error kTailRel
+  const double tail_abs = a.top_p * (kTailRel * tail + 1e-30);
+  const double target_p = a.top_p * z, lo = target_p * (1.0 - rel) - tail_abs, hi = target_p * (1.0 + rel) + tail_abs;
   if (tid == 0) found_at = 0x7fffffff;
   __syncthreads();
   {
@@ -423,8 +487,8 @@ __global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
   const int pos = found_at;
   // mass_before >= lo: the crossing is (or may be) before the window; pos unset: not reached inside it
   ok = ok && mass_before < lo && pos != 0x7fffffff;
-  if (!ok) {  // uniform in the CTA: the other paths redo the row
-    if (tid == 0) { a.tokens[row] = -1; a.status[row] = -8; }
+  if (!ok) {  // uniform in the CTA: the cluster kernel redoes the row (the nucleus is wide: no candidate set covers it)
+    if (tid == 0) { a.tokens[row] = -1; a.status[row] = kNeedsCluster; }
     return;
   }
   if ((pos >> 1) == tid) {
@@ -440,9 +504,13 @@ __global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
   for (int i = 0; i < 2; ++i)
     if (2 * tid + i <= pos) atomicAdd(&ksum[ids[i] / kFlatSub], e[i]);
   __syncthreads();
+  if (cut_amb) {  // inside the (FP32-class) bound: the cluster kernel decides the row with FP64 sums throughout
+    if (tid == 0) { a.tokens[row] = -1; a.status[row] = kNeedsCluster; }
+    return;
+  }
   const Cut cut{cut_y, cut_id};
   const int kept = n_before + pos + 1;
-  int status = cut_amb ? 2 : 0;
+  int status = 0;
   // ---- inverse CDF in id order (sampling.cpp:18-21): sub-region that holds u * total, then its ids one by one
   const double k0 = tid < kFlatSubs / 2 ? ksum[2 * tid] : 0.0, k1 = tid < kFlatSubs / 2 ? ksum[2 * tid + 1] : 0.0;
   const double pre0 = flat_prefix2(red, k0, k1), pre1 = pre0 + k1;  // kept mass through sub-region 2*tid (and 2*tid+1)
@@ -520,7 +588,19 @@ __global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
   (void)lane;
 }
 
+__global__ void tail_probe_kernel(const float *y, TailExp k, float *out, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = tail_weight(y[i], k);
+}
+
 }  // namespace
+
+cudaError_t launch_tail_probe(const float *y, float m, double t, float *out, int n, cudaStream_t stream) {
+  const double c64 = 1.4426950408889634074 / t;
+  const TailExp k{m, float(c64), float(c64 - double(float(c64)))};
+  tail_probe_kernel<<<(n + 255) / 256, 256, 0, stream>>>(y, k, out, n);
+  return cudaGetLastError();
+}
 
 size_t flat_scratch_bytes(int rows) {
   size_t per_row = kFlatChunks * sizeof(FlatPartial) + kFlatBins * (sizeof(unsigned) + sizeof(unsigned long long)) +
@@ -534,7 +614,7 @@ cudaError_t launch_flat(FlatArgs a, void *scratch, cudaStream_t stream) {
   unsigned char *p = static_cast<unsigned char *>(scratch);
   const size_t rows = size_t(a.rows);
   a.s.hmass = reinterpret_cast<unsigned long long *>(p); p += rows * kFlatBins * sizeof(unsigned long long);
-  a.s.hcount = reinterpret_cast<unsigned *>(p); p += rows * kFlatBins * sizeof(unsigned);  // (kept for layout; unused)
+  a.s.subtail = reinterpret_cast<double *>(p); p += rows * kFlatBins * sizeof(unsigned);  // rows * kFlatSubs doubles fit
   a.s.lcount = reinterpret_cast<int *>(p); p += rows * 4 * sizeof(int);
   const size_t zeroed = size_t(p - static_cast<unsigned char *>(scratch));
   a.s.lkeys = reinterpret_cast<unsigned long long *>(p); p += rows * kFlatList * sizeof(unsigned long long);

@@ -16,15 +16,18 @@ constexpr int kFlatList = 1024;     // ids of the window that can be sorted exac
 constexpr int kFlatMinNucleus = 512;  // nuclei that certainly hold fewer ids are the other paths' case
 constexpr int kFlatMinRows = 64;    // below this batch size a cluster per row is faster
 constexpr int kFlatMinVocab = 16384;
+// internal status word: the row has a wide nucleus but this path could not certify it; only the cluster kernel may
+// take it (the streaming path's candidate sets never cover such a row).  Never returned to the caller.
+constexpr int kNeedsCluster = -9;
 
 struct FlatPartial { float max, min; int argmax, flags; };
 struct FlatInfo { float max, min; int argmax, applicable, w0, w1, pad0, pad1; };
 struct FlatScratch {
   FlatPartial *partial;        // [rows][kFlatChunks]
-  unsigned *hcount;            // [rows][kFlatBins]
+  double *subtail;             // [rows][kFlatSubs]: FP32-class part of subz (ids beyond the window)
   unsigned long long *hmass;   // [rows][kFlatBins], fixed point relative to the bin's near edge
   FlatInfo *info;              // [rows]
-  double *subz, *subsure;      // [rows][kFlatSubs]
+  double *subz, *subsure;      // [rows][kFlatSubs]: normaliser part, mass of the ids before the window
   int *subcnt;                 // [rows][kFlatSubs]
   int *lcount;                 // [rows][4]: window list length, "a 32-bit mass may have wrapped" flag
   unsigned long long *lkeys;   // [rows][kFlatList]

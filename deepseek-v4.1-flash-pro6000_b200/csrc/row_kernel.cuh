@@ -174,7 +174,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
   const int row = blockIdx.x / c.nranks;
   if (a.only_uncovered) {  // same answer in every CTA of the cluster, so the whole cluster leaves together
     const int st = kMode == kModeSample ? a.status[row] : a.stats[row].status;
-    if (st != -8) return;
+    if (st != -8 && st != -9) return;  // -9: handed on by the batch path for wide nuclei (flat.cuh)
   }
   const float *logits = a.logits + size_t(row) * a.logits_stride;
 

@@ -136,6 +136,13 @@ __global__ void exp_probe_kernel(const double *x, double *out, int n) {
 }
 }  // namespace ds41
 
+namespace ds41 { cudaError_t launch_tail_probe(const float *y, float m, double t, float *out, int n, cudaStream_t stream); }
+extern "C" int ds41_b200_test_tail_weight(const float *y, float max_logit, double temperature, float *out, int n,
+                                          cudaStream_t stream) {
+  if (!y || !out || n < 1 || !(temperature > 0)) return invalid("tail probe arguments");
+  return int(ds41::launch_tail_probe(y, max_logit, temperature, out, n, stream));
+}
+
 extern "C" int ds41_b200_test_exp_nonpos(const double *x, double *out, int n, cudaStream_t stream) {
   if (!x || !out || n < 1) return invalid("exp probe arguments");
   ds41::exp_probe_kernel<<<(n + 255) / 256, 256, 0, stream>>>(x, out, n);
