@@ -160,7 +160,6 @@ class HeadSample:
         # would also enable, only covers peaked distributions)
         self.scratch = torch.empty(pkg.sample_scratch_bytes(batch, VOCAB), dtype=torch.uint8, device=device) if batch >= 64 else None
         self.units = batch
-        self.launches_per_step = 3
         self.h2d, self.d2h = batch * HIDDEN * 2, batch * 4
         # the two kernels that can dominate a step, each timed with its own event pair
         head_bytes = self.vn * HIDDEN + self.ws.numel() * 4 + batch * HIDDEN + batch * 32 * 4 + batch * self.vn * 4
@@ -174,10 +173,17 @@ class HeadSample:
         }
         self.graph = None
         self.sharded = None
+        self.exchange_note = None
+        # own kernels per step: quantise, head, then the sampler call = flat_stats/hist/window/mass/resolve + the three
+        # predicated fall-through kernels (chunk, combine, row_kernel) for batches >= 64, else row_kernel alone
+        self.launches_per_step = 10 if batch >= 64 else 3
         if world > 1:
             self.sharded = import_module("ds41_b200.sharded").ShardedDecodeTail(pkg, device, batch, self.v0, self.vn,
                                                                               VOCAB, temperature, top_p, strategy)
-            self.launches_per_step = 3 if strategy == "rows" else 4
+            strategy = self.sharded.strategy  # "candidates" if the peer buffers could not be mapped
+            self.exchange_note = self.sharded.exchange_error
+            local_rows = -(-batch // world)
+            self.launches_per_step = (10 if local_rows >= 64 else 5) if strategy == "rows" else 6
 
     def step(self, i, hidden=None, ev=None):
         pkg = self.pkg
@@ -613,6 +619,8 @@ def main():
                 "launch": "one CUDA graph replay per step" if world == 1 else "eager launches (host checks the coverage flag every step)"}
         if same_as_single is not None:
             line["tokens_equal_single_gpu_path"] = same_as_single
+        if getattr(wl, "exchange_note", None):
+            line["config"]["exchange"] = "candidates (fallback: " + wl.exchange_note + ")"
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline(name)
         print(json.dumps(line))

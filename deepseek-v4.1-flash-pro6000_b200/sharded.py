@@ -152,6 +152,10 @@ def rows_plan(rows, world):
     return per, [(min(rows, r * per), max(0, min(rows, (r + 1) * per) - min(rows, r * per))) for r in range(world)]
 
 
+class PeerMappingUnavailable(RuntimeError):
+    """Raised on EVERY rank when some rank could not allocate or map the peer-visible buffers."""
+
+
 class RowExchange:
     """One peer-visible full-vocabulary logits buffer [rows_per_owner, vocab] per rank, mapped into every rank."""
 
@@ -170,16 +174,20 @@ class RowExchange:
                                                                       C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                                                       C.c_void_p]
         self._lib = lib
+        # Every rank must end up with the same verdict (a rank that raised alone would leave the others waiting in the
+        # next collective): failures are recorded, agreed on with one all-reduce, and only then raised everywhere.
+        failure = None
         handle = C.create_string_buffer(64)
         mine = C.c_void_p()
         with torch.cuda.device(device):
             rc = lib.ds41_b200_peer_alloc(self.rows_per_owner * vocab * 4, C.byref(mine), handle)
         if rc:
-            raise RuntimeError(f"ds41_b200_peer_alloc: cudaError {rc} ({pkg.last_error()})")
-        self._mine = mine
+            failure = f"ds41_b200_peer_alloc: cudaError {rc} ({pkg.last_error()})"
+            mine = C.c_void_p()
+        self._mine = mine if mine.value else None
         handles = [None] * self.world
         if self.world > 1:
-            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            dist.all_gather_object(handles, bytes(handle.raw) if not failure else None, group=group)
         else:
             handles[0] = bytes(handle.raw)
         self._opened = []
@@ -188,13 +196,26 @@ class RowExchange:
             if r == self.rank:
                 ptrs.append(mine.value)
                 continue
+            if h is None or failure:
+                failure = failure or f"rank {r} could not allocate its buffer"
+                continue
             p = C.c_void_p()
             with torch.cuda.device(device):
                 rc = lib.ds41_b200_peer_open(C.create_string_buffer(h, 64), C.byref(p))
             if rc:
-                raise RuntimeError(f"ds41_b200_peer_open(rank {r}): cudaError {rc} ({pkg.last_error()})")
+                failure = f"ds41_b200_peer_open(rank {r}): cudaError {rc} ({pkg.last_error()})"
+                continue
             self._opened.append(p)
             ptrs.append(p.value)
+        if self.world > 1:
+            verdict = torch.tensor([0 if failure else 1], dtype=torch.int32, device=device)
+            dist.all_reduce(verdict, op=dist.ReduceOp.MIN, group=group)
+            if verdict.item() == 0:
+                failure = failure or "another rank could not map the peer buffers"
+        if failure:
+            self.full = None
+            self.close()
+            raise PeerMappingUnavailable(failure)
         self.owner_ptrs = (C.c_void_p * self.world)(*ptrs)
         self.full = torch.as_tensor(_DeviceBlock(mine.value, (self.rows_per_owner, vocab), "<f4"), device=device)
         self.full.zero_()
@@ -244,7 +265,7 @@ class RowExchange:
         for p in self._opened:
             self._lib.ds41_b200_peer_close(p)
         self._opened = []
-        if self._mine is not None:
+        if getattr(self, "_mine", None) is not None:
             self.full = None
             self._lib.ds41_b200_peer_free(self._mine)
             self._mine = None
@@ -261,7 +282,13 @@ class ShardedDecodeTail:
         self.pkg, self.device, self.rows, self.v0, self.vn, self.vocab = pkg, device, rows, vocab_offset, vocab_local, vocab
         self.t, self.top_p, self.strategy, self.probe_every = temperature, top_p, strategy, probe_every
         self.rows_mode_left = 0
-        self.exchange = RowExchange(pkg, device, rows, vocab, group) if strategy != "candidates" else None
+        self.exchange, self.exchange_error = None, None
+        if strategy != "candidates":
+            try:
+                self.exchange = RowExchange(pkg, device, rows, vocab, group)
+            except PeerMappingUnavailable as exc:  # the same on every rank: fall back to the NCCL-only exchange
+                self.exchange_error = str(exc)
+                self.strategy = strategy = "candidates"
         self.cands = None
         if strategy != "rows":
             self.cands = ShardedSampler(pkg, torch, device, rows, vocab_offset, vocab_local, vocab, temperature, top_p, group)
