@@ -1,13 +1,13 @@
 // Batch path of the sampler for WIDE nuclei (flat distributions) at batch sizes where a thread-block cluster per row
 // leaves the GPU idle most of the time: the wide-nucleus algorithm of row_wide.cuh restated as five grid-wide kernels
 // over the whole batch, so that every pass runs at full occupancy.
-//   flat_stats_kernel   (row, quarter row)  maximum (first), minimum, finiteness                         -> FlatPartial
-//   flat_hist_kernel    (row, quarter row)  1024-bin histogram over the row's range: exact counts and fixed-point
+//   flat_stats_kernel   (row, 1/4 or 1/8 row)  maximum (first), minimum, finiteness                         -> FlatPartial
+//   flat_hist_kernel    (row, 1/4 or 1/8 row) 1024-bin histogram over the row's range: exact counts and fixed-point
 //                                           FP32-class masses, shared memory first, then global integer atomics
 //   flat_window_kernel  (row)               error-bracketed running mass -> the window of bins that holds the top-p
 //                                           crossing; rows this path does not fit get status -8 (the caller sends
 //                                           them to the other paths), non-finite rows -1
-//   flat_mass_kernel    (row, quarter row)  the one FP64 pass: per 1024-id sub-region the normaliser part, the mass
+//   flat_mass_kernel    (row, 1/4 or 1/8 row) the one FP64 pass: per 1024-id sub-region the normaliser part, the mass
 //                                           and count of the ids before the window; the window's ids to a per-row list
 //   flat_resolve_kernel (row)               sorts the list exactly, FP64 prefix sums -> certified cut; kept mass per
 //                                           sub-region -> the sub-region that holds u * total -> walks its 1024 ids
@@ -75,13 +75,14 @@ __device__ __forceinline__ double flat_sum(FlatRed &r, double v) {
 
 // ids [begin, end) of this CTA's quarter row
 __device__ __forceinline__ void quarter(const FlatArgs &a, int chunk, int *begin, int *end) {
-  *begin = min(a.vocab, chunk * kFlatChunkIds);
-  *end = min(a.vocab, *begin + kFlatChunkIds);
+  const int ids = kFlatSub * (kFlatSubs / a.chunks);
+  *begin = min(a.vocab, chunk * ids);
+  *end = min(a.vocab, *begin + ids);
 }
 
 __global__ void __launch_bounds__(kFT) flat_stats_kernel(FlatArgs a) {
   __shared__ FlatRed red;
-  const int row = blockIdx.x / kFlatChunks, chunk = blockIdx.x % kFlatChunks;
+  const int row = blockIdx.x / a.chunks, chunk = blockIdx.x % a.chunks;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int begin, end;
   quarter(a, chunk, &begin, &end);
@@ -115,15 +116,15 @@ __global__ void __launch_bounds__(kFT) flat_stats_kernel(FlatArgs a) {
       lowest = fminf(lowest, red.g[w]);
       flags |= red.j[w];
     }
-    a.s.partial[row * kFlatChunks + chunk] = FlatPartial{best, lowest, best_id, flags};
+    a.s.partial[row * kFlatMaxChunks + chunk] = FlatPartial{best, lowest, best_id, flags};
   }
 }
 
 // Row maximum (first), minimum and flags from the quarter rows' partial results; the same in every thread.
 __device__ __forceinline__ FlatPartial row_extremes(const FlatArgs &a, int row) {
-  FlatPartial r = a.s.partial[row * kFlatChunks];
-  for (int c = 1; c < kFlatChunks; ++c) {
-    const FlatPartial p = a.s.partial[row * kFlatChunks + c];
+  FlatPartial r = a.s.partial[row * kFlatMaxChunks];
+  for (int c = 1; c < a.chunks; ++c) {
+    const FlatPartial p = a.s.partial[row * kFlatMaxChunks + c];
     if (p.max > r.max || (p.max == r.max && p.argmax < r.argmax)) { r.max = p.max; r.argmax = p.argmax; }
     r.min = fminf(r.min, p.min);
     r.flags |= p.flags;
@@ -152,7 +153,7 @@ constexpr double kQInv = 1.0 / 131072.0;
 
 __global__ void __launch_bounds__(kFT) flat_hist_kernel(FlatArgs a) {
   __shared__ unsigned qmass[kFlatBins];
-  const int row = blockIdx.x / kFlatChunks, chunk = blockIdx.x % kFlatChunks;
+  const int row = blockIdx.x / a.chunks, chunk = blockIdx.x % a.chunks;
   const FlatPartial ext = row_extremes(a, row);
   if (ext.flags || !(ext.min < ext.max)) return;  // the window kernel reports the row
   const FlatBins b = make_bins(ext, a.t);
@@ -274,7 +275,7 @@ __global__ void __launch_bounds__(kFT, 2) flat_mass_kernel(FlatArgs a) {
   // per-warp queue of the ids that need an FP64 weight (before or inside the window): position in the sub-region
   __shared__ float queue_y[kFW][256];
   __shared__ unsigned short queue_at[kFW][256];
-  const int row = blockIdx.x / kFlatChunks, chunk = blockIdx.x % kFlatChunks;
+  const int row = blockIdx.x / a.chunks, chunk = blockIdx.x % a.chunks;
   const FlatInfo info = a.s.info[row];
   if (!info.applicable) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -285,10 +286,10 @@ __global__ void __launch_bounds__(kFT, 2) flat_mass_kernel(FlatArgs a) {
   const double c64 = 1.4426950408889634074 / a.t;
   const TailExp tail{info.max, float(c64), float(c64 - double(float(c64)))};
   const float *x = a.logits + size_t(row) * a.stride;
-  constexpr int kSubsPerWarp = kFlatSubs / kFlatChunks / kFW;  // 2
+  const int subs_per_warp = kFlatSubs / a.chunks / kFW;  // 2 or 1
 #pragma unroll 1
-  for (int s = 0; s < kSubsPerWarp; ++s) {
-    const int sub = chunk * (kFlatSubs / kFlatChunks) + warp * kSubsPerWarp + s;
+  for (int s = 0; s < subs_per_warp; ++s) {
+    const int sub = chunk * (kFlatSubs / a.chunks) + warp * subs_per_warp + s;
     const int base = sub * kFlatSub;
     double z = 0, sure_mass = 0;
     int sure_count = 0;
@@ -603,7 +604,7 @@ cudaError_t launch_tail_probe(const float *y, float m, double t, float *out, int
 }
 
 size_t flat_scratch_bytes(int rows) {
-  size_t per_row = kFlatChunks * sizeof(FlatPartial) + kFlatBins * (sizeof(unsigned) + sizeof(unsigned long long)) +
+  size_t per_row = kFlatMaxChunks * sizeof(FlatPartial) + kFlatBins * (sizeof(unsigned) + sizeof(unsigned long long)) +
                    sizeof(FlatInfo) + kFlatSubs * (2 * sizeof(double) + sizeof(int)) + 4 * sizeof(int) +
                    kFlatList * sizeof(unsigned long long);
   return size_t(rows) * per_row + 256;
@@ -621,14 +622,15 @@ cudaError_t launch_flat(FlatArgs a, void *scratch, cudaStream_t stream) {
   a.s.subz = reinterpret_cast<double *>(p); p += rows * kFlatSubs * sizeof(double);
   a.s.subsure = reinterpret_cast<double *>(p); p += rows * kFlatSubs * sizeof(double);
   a.s.info = reinterpret_cast<FlatInfo *>(p); p += rows * sizeof(FlatInfo);
-  a.s.partial = reinterpret_cast<FlatPartial *>(p); p += rows * kFlatChunks * sizeof(FlatPartial);
+  a.s.partial = reinterpret_cast<FlatPartial *>(p); p += rows * kFlatMaxChunks * sizeof(FlatPartial);
   a.s.subcnt = reinterpret_cast<int *>(p);
   cudaError_t e = cudaMemsetAsync(scratch, 0, zeroed, stream);
   if (e != cudaSuccess) return e;
-  flat_stats_kernel<<<a.rows * kFlatChunks, kFT, 0, stream>>>(a);
-  flat_hist_kernel<<<a.rows * kFlatChunks, kFT, 0, stream>>>(a);
+  a.chunks = a.rows >= 512 ? 4 : 8;  // fewer rows: more, shorter CTAs per row
+  flat_stats_kernel<<<a.rows * a.chunks, kFT, 0, stream>>>(a);
+  flat_hist_kernel<<<a.rows * a.chunks, kFT, 0, stream>>>(a);
   flat_window_kernel<<<a.rows, kFT, 0, stream>>>(a);
-  flat_mass_kernel<<<a.rows * kFlatChunks, kFT, 0, stream>>>(a);
+  flat_mass_kernel<<<a.rows * a.chunks, kFT, 0, stream>>>(a);
   flat_resolve_kernel<<<a.rows, kFT, 0, stream>>>(a);
   return cudaGetLastError();
 }

@@ -6,15 +6,14 @@
 
 namespace ds41 {
 
-constexpr int kFlatChunks = 4;      // CTAs per row in the streaming passes (a quarter row each)
+constexpr int kFlatMaxChunks = 8;   // CTAs per row in the streaming passes: 4 (large batches) or 8 (fewer rows, shorter CTAs)
 constexpr int kFlatThreads = 512;
 constexpr int kFlatSub = 1024;      // ids per sub-region: the granularity of the inverse-CDF search
 constexpr int kFlatSubs = 128;      // sub-regions per row (covers the largest vocabulary, 131072)
-constexpr int kFlatChunkIds = kFlatSub * (kFlatSubs / kFlatChunks);
 constexpr int kFlatBins = 1024;
 constexpr int kFlatList = 1024;     // ids of the window that can be sorted exactly
 constexpr int kFlatMinNucleus = 512;  // nuclei that certainly hold fewer ids are the other paths' case
-constexpr int kFlatMinRows = 64;    // below this batch size a cluster per row is faster
+constexpr int kFlatMinRows = 192;   // below this batch size a cluster per row is as fast or faster (measured: equal near 128-256 rows)
 constexpr int kFlatMinVocab = 16384;
 // internal status word: the row has a wide nucleus but this path could not certify it; only the cluster kernel may
 // take it (the streaming path's candidate sets never cover such a row).  Never returned to the caller.
@@ -23,7 +22,7 @@ constexpr int kNeedsCluster = -9;
 struct FlatPartial { float max, min; int argmax, flags; };
 struct FlatInfo { float max, min; int argmax, applicable, w0, w1, pad0, pad1; };
 struct FlatScratch {
-  FlatPartial *partial;        // [rows][kFlatChunks]
+  FlatPartial *partial;        // [rows][kFlatMaxChunks]
   double *subtail;             // [rows][kFlatSubs]: FP32-class part of subz (ids beyond the window)
   unsigned long long *hmass;   // [rows][kFlatBins], fixed point relative to the bin's near edge
   FlatInfo *info;              // [rows]
@@ -36,6 +35,7 @@ struct FlatArgs {
   const float *logits;         // rows 16-byte aligned: base and stride
   long long stride;
   int vocab, rows;
+  int chunks;                  // 4 or 8 (set by launch_flat)
   double t, top_p;             // t > 0, top_p < 1
   const uint64_t *seeds, *steps;
   uint32_t slot, purpose;

@@ -46,7 +46,7 @@ def answered_by_batch_path(pkg, scratch, rows, vocab):
 
 @pytest.mark.parametrize("t,top", [(0.6, 0.95), (1.0, 0.95), (0.6, 0.5), (1.3, 0.99), (0.25, 0.9)])
 def test_flat_rows_match_oracle(pkg, oracle, t, top):
-    rows = 96
+    rows = 200
     x = oracle.gen_normal(11, int(t * 100), (rows, V), 1.28)
     seeds, steps = np.arange(rows) * 31 + 5, np.arange(rows) + 1000
     want, wst = oracle.sample_rows(x, t, top, seeds, steps, slot=1, purpose=0, threads=8)
@@ -61,7 +61,7 @@ def test_flat_rows_match_oracle(pkg, oracle, t, top):
 
 def test_mixed_batch_falls_through_per_row(pkg, oracle):
     """Flat rows, peaked rows (nucleus of a few ids) and rows with one towering logit in one batch."""
-    rows = 80
+    rows = 208
     x = oracle.gen_normal(12, 0, (rows, V), 1.28)
     x[1::4] = oracle.gen_logits(77, rows // 4, V)          # Zipf + Gaussian: peaked
     x[2::8, 777] = 40.0                                     # one id holds all the mass: nucleus of one
@@ -75,7 +75,7 @@ def test_mixed_batch_falls_through_per_row(pkg, oracle):
 
 
 def test_nonfinite_rows_and_ragged_stride(pkg, oracle):
-    rows, vocab, stride = 64, 40001, 40004
+    rows, vocab, stride = 192, 40001, 40004
     buf = np.zeros((rows, stride), np.float32)
     buf[:, :vocab] = oracle.gen_normal(13, 0, (rows, vocab), 1.0)
     bad = [3, 17, 40]
