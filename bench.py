@@ -232,10 +232,36 @@ class HeadSample:
         self.graph.replay()
 
     def e2e_step(self, i):
-        self.hidden.copy_(self.host_ring[i % len(self.host_ring)], non_blocking=True)
+        """One step from pinned host memory to token ids on the host.  The host->device copy of the NEXT step's hidden
+        states runs on a side stream while this step computes (two staging buffers), as a serving loop would prefetch
+        its next batch; every step still copies its own inputs in and its tokens out, and the host waits for the
+        tokens of step i before it returns."""
+        torch = self.torch
+        main = torch.cuda.current_stream()
+        if not hasattr(self, "copy_stream"):
+            self.copy_stream = torch.cuda.Stream(device=self.device)
+            self.staging = [torch.empty_like(self.hidden), torch.empty_like(self.hidden)]
+            self.staged = [torch.cuda.Event(), torch.cuda.Event()]
+            self.consumed = [torch.cuda.Event(), torch.cuda.Event()]
+            self.prefetched = None
+        def prefetch(step):
+            slot = step % 2
+            with torch.cuda.stream(self.copy_stream):
+                self.copy_stream.wait_event(self.consumed[slot])  # the step that last used this buffer has read it
+                self.staging[slot].copy_(self.host_ring[step % len(self.host_ring)], non_blocking=True)
+                self.staged[slot].record(self.copy_stream)
+            self.prefetched = step
+        if self.prefetched != i:
+            self.consumed[i % 2].record(main)
+            prefetch(i)
+        slot = i % 2
+        main.wait_event(self.staged[slot])
+        self.hidden.copy_(self.staging[slot], non_blocking=True)
+        self.consumed[slot].record(main)
+        prefetch(i + 1)
         self.graph_step(i, from_host=True)
         self.tokens_host.copy_(self.tokens, non_blocking=True)
-        self.torch.cuda.current_stream().synchronize()
+        main.synchronize()
         return self.tokens_host
 
     def check(self):
