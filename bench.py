@@ -33,11 +33,17 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised
 # under profiles/ (None = not captured yet)
 NCU_TRAFFIC = {
-    # head_fp8_kernel<64,1>, cfg2_b64: 531.43 MB read + 35.58 MB written (profiles/head_fp8_kernel_cfg2_b64.md)
-    ("cfg2_b64", "head_fp8_kernel"): 567.0e6,
-    # row_kernel<0>, cfg2_b64: 33.19 MB read + 256 B written (profiles/row_kernel_cfg2_b64.md)
-    ("cfg2_b1", "sampler"): 33.19e6 / 64,
-    # batch path of the sampler (flat_* kernels): see profiles/sampler_flat_*.md
+    # head_fp8_kernel<64,128>, 64 x 129280 x 4096: 530.38 MB read + 28.19 MB written (profiles/head_fp8_kernel_b64_full_vocab.md)
+    ("cfg2_b64", "head_fp8_kernel"): 558.6e6,
+    # row_kernel<0>, 64 flat rows: 33.195 MB read + 256 B written (profiles/row_kernel_64rows_flat.md); one read per row
+    ("cfg2_b64", "sampler"): 33.195e6,
+    ("cfg2_b8", "sampler"): 33.195e6 / 8,
+    ("cfg2_b1", "sampler"): 33.195e6 / 64,
+    # batch path of the sampler at 1024 rows: three passes over the logits by construction (flat_stats, flat_hist,
+    # flat_mass); the FP64 pass was captured at 256 rows (132.42 MB read + 4.21 MB written = its algorithmic bytes,
+    # profiles/flat_mass_kernel_256rows.md) and traffic grows in proportion to the rows, so per 1024 rows:
+    # 3 x 529.7 MB read + 16.8 MB written
+    ("cfg5_b1024", "sampler"): 3 * 529.7e6 + 16.8e6,
 }
 
 
