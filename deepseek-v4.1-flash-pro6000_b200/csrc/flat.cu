@@ -346,28 +346,38 @@ __global__ void __launch_bounds__(kFT, 2) flat_mass_kernel(FlatArgs a) {
     for (int j = 0; j < kFlatSub / 128; ++j) {
       const float4 nxt = j + 1 < kFlatSub / 128 ? fetch(j + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
       const float ys4[4] = {cur.x, cur.y, cur.z, cur.w};
+      const int at0 = (j * 32 + lane) * 4;
+      // ids up to the window's far edge go to the FP64 queue, the others are tail; the lane's (up to four) queue
+      // entries are placed with one warp-wide prefix of the lanes' counts (three votes on the bits of the count)
+      int mine = 0;
+      bool near[4];
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
-        const int at = (j * 32 + lane) * 4 + q4;
         const float y = ys4[q4];
-        const bool valid = base + at < a.vocab;
-        // ids up to the window's far edge go to the FP64 queue, the others are tail
-        const bool near = valid && (b.m - y) * b.inv_w < edge1;
-        if (valid && !near) {
+        const bool valid = base + at0 + q4 < a.vocab;
+        near[q4] = valid && (b.m - y) * b.inv_w < edge1;
+        mine += near[q4] ? 1 : 0;
+        if (valid && !near[q4]) {
           const float w = tail_weight(y, tail);
           const float t1 = __fsub_rn(w, tail_comp), t2 = __fadd_rn(tail_sum, t1);
           tail_comp = __fsub_rn(__fsub_rn(t2, tail_sum), t1);
           tail_sum = t2;
         }
-        const unsigned ballot = __ballot_sync(0xffffffffu, near);
-        if (near) {
-          const int slot = (head + count + __popc(ballot & ((1u << lane) - 1u))) & 255;
-          queue_y[warp][slot] = y;
-          queue_at[warp][slot] = (unsigned short)at;
-        }
-        count += __popc(ballot);
-        __syncwarp();
       }
+      const unsigned below = (1u << lane) - 1u;
+      const unsigned v1 = __ballot_sync(0xffffffffu, mine & 1), v2 = __ballot_sync(0xffffffffu, mine & 2),
+                     v4 = __ballot_sync(0xffffffffu, mine & 4);
+      int slot = head + count + __popc(v1 & below) + 2 * __popc(v2 & below) + 4 * __popc(v4 & below);
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        if (near[q4]) {
+          queue_y[warp][slot & 255] = ys4[q4];
+          queue_at[warp][slot & 255] = (unsigned short)(at0 + q4);
+          ++slot;
+        }
+      }
+      count += __popc(v1) + 2 * __popc(v2) + 4 * __popc(v4);
+      __syncwarp();
       while (count >= 32) drain(32);
       cur = nxt;
     }
