@@ -483,45 +483,67 @@ __global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
   }
   const double through0 = mass_before + flat_prefix2(red, e[0], e[1]), through1 = through0 + e[1];
   const double rel = 2.0 * (double(a.vocab) + 256.0) * kU;
-  // the ids beyond the window entered z with FP32-class weights: their share of z carries a relative error kTailRel
-  const double tail_abs = a.top_p * (kTailRel * tail + 1e-30);
-  const double target_p = a.top_p * z, lo = target_p * (1.0 - rel) - tail_abs, hi = target_p * (1.0 + rel) + tail_abs;
-  if (tid == 0) found_at = 0x7fffffff;
-  __syncthreads();
-  {
-    int mine = -1;
-    if (2 * tid < n && through0 >= target_p) mine = 2 * tid;
-    else if (2 * tid + 1 < n && through1 >= target_p) mine = 2 * tid + 1;
-    if (mine >= 0) atomicMin(&found_at, mine);
+  // Two attempts at the crossing.  First with the normaliser as the mass pass left it: the ids beyond the window entered
+  // it with FP32-class weights, so their share of z carries a relative error kTailRel.  If the crossing falls inside
+  // that wider bound (about one row in a hundred), this CTA recomputes the tail of its row with FP64 weights and
+  // decides again with the FP64 bound alone.
+  const FlatBins b = make_bins(FlatPartial{info.max, info.min, info.argmax, 0}, a.t);
+  const float edge1 = info.w1 >= kFlatBins - 1 ? CUDART_INF_F : float(info.w1 + 1);
+  double tail_abs = a.top_p * (kTailRel * tail + 1e-30);
+  int pos = 0x7fffffff;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    const double target_p = a.top_p * z, lo = target_p * (1.0 - rel) - tail_abs, hi = target_p * (1.0 + rel) + tail_abs;
+    if (tid == 0) { found_at = 0x7fffffff; cut_amb = 0; }
+    __syncthreads();
+    {
+      int mine = -1;
+      if (2 * tid < n && through0 >= target_p) mine = 2 * tid;
+      else if (2 * tid + 1 < n && through1 >= target_p) mine = 2 * tid + 1;
+      if (mine >= 0) atomicMin(&found_at, mine);
+    }
+    __syncthreads();
+    pos = found_at;
+    // mass_before >= lo: the crossing is (or may be) before the window; pos unset: not reached inside it
+    if (!(ok && mass_before < lo && pos != 0x7fffffff)) { ok = false; break; }
+    if ((pos >> 1) == tid) {
+      const int i = pos & 1;
+      const double mass_at = i ? through1 : through0, prev_at = mass_at - e[i];
+      cut_amb = ((mass_at < hi) || (prev_at >= lo)) ? 1 : 0;
+      cut_y = ys[i]; cut_id = ids[i];
+      cut_mass[0] = mass_at;
+    }
+    __syncthreads();
+    if (!cut_amb || attempt == 1) break;
+    // FP64 weights of the ids beyond the window (the same predicate as the mass pass)
+    double exact = 0;
+    auto add_tail = [&](float y) {
+      const double w = exp_nonpos((double(y) - m64) * inv_t);  // unconditional: independent calls overlap
+      exact += ((b.m - y) * b.inv_w < edge1) ? 0.0 : w;
+    };
+    const int vec_end = a.vocab & ~3;  // rows are 16-byte aligned
+#pragma unroll 2
+    for (int id = 4 * tid; id < vec_end; id += 4 * kFT) {
+      const float4 v = __ldg(reinterpret_cast<const float4 *>(x + id));
+      add_tail(v.x); add_tail(v.y); add_tail(v.z); add_tail(v.w);
+    }
+    for (int id = vec_end + tid; id < a.vocab; id += kFT) add_tail(__ldg(x + id));
+    exact = flat_sum(red, exact);
+    z = (z - tail) + exact;
+    tail_abs = 0;
   }
-  __syncthreads();
-  const int pos = found_at;
-  // mass_before >= lo: the crossing is (or may be) before the window; pos unset: not reached inside it
-  ok = ok && mass_before < lo && pos != 0x7fffffff;
   if (!ok) {  // uniform in the CTA: the cluster kernel redoes the row (the nucleus is wide: no candidate set covers it)
     if (tid == 0) { a.tokens[row] = -1; a.status[row] = kNeedsCluster; }
     return;
   }
-  if ((pos >> 1) == tid) {
-    const int i = pos & 1;
-    const double mass_at = i ? through1 : through0, prev_at = mass_at - e[i];
-    cut_amb = ((mass_at < hi) || (prev_at >= lo)) ? 1 : 0;
-    cut_y = ys[i]; cut_id = ids[i];
-    cut_mass[0] = mass_at;
-  }
-  __syncthreads();
+  const int uncertified_cut = cut_amb;  // still inside the FP64 bound: decided, flagged like every other path does
   // kept mass per sub-region: the ids before the window plus the window's ids up to the cut
 #pragma unroll
   for (int i = 0; i < 2; ++i)
     if (2 * tid + i <= pos) atomicAdd(&ksum[ids[i] / kFlatSub], e[i]);
   __syncthreads();
-  if (cut_amb) {  // inside the (FP32-class) bound: the cluster kernel decides the row with FP64 sums throughout
-    if (tid == 0) { a.tokens[row] = -1; a.status[row] = kNeedsCluster; }
-    return;
-  }
   const Cut cut{cut_y, cut_id};
   const int kept = n_before + pos + 1;
-  int status = 0;
+  int status = uncertified_cut ? 2 : 0;
   // ---- inverse CDF in id order (sampling.cpp:18-21): sub-region that holds u * total, then its ids one by one
   const double k0 = tid < kFlatSubs / 2 ? ksum[2 * tid] : 0.0, k1 = tid < kFlatSubs / 2 ? ksum[2 * tid + 1] : 0.0;
   const double pre0 = flat_prefix2(red, k0, k1), pre1 = pre0 + k1;  // kept mass through sub-region 2*tid (and 2*tid+1)

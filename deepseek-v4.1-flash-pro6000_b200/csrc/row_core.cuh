@@ -172,6 +172,7 @@ struct RowCtx {
   int begin, len;         // this CTA's slice [begin, begin+len)
   int region;             // ids per warp region (multiple of 32): warp w owns local [w*region, (w+1)*region)
   int xphase;
+  int timed_out;          // a staging copy of the row just processed did not land (the same in every CTA of the cluster)
 };
 
 __device__ __forceinline__ RowCtx make_ctx(RowSmem *s, int vocab) {
@@ -185,6 +186,7 @@ __device__ __forceinline__ RowCtx make_ctx(RowSmem *s, int vocab) {
   c.len = min(vocab, c.begin + c.stride_ids) - c.begin;
   c.region = (((c.stride_ids + kWarps - 1) / kWarps) + 31) & ~31;
   c.xphase = 0;
+  c.timed_out = 0;
   return c;
 }
 
@@ -318,6 +320,9 @@ __device__ __forceinline__ bool stage_wait(RowCtx &c, bool used_tma) {
     ok = done != 0;
   }
   __syncthreads();
+  // the barrier object is initialised again for the cluster's next row (not after a timeout: the copy may still
+  // signal it, and the cluster then takes no further row)
+  if (c.tid == 0 && used_tma && ok) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(&c.s->mbar)) : "memory");
   return ok;
 }
 

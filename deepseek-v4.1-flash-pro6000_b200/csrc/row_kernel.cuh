@@ -28,6 +28,7 @@ struct RowArgs {
   int32_t *status;
   RowStats *stats;
   int only_uncovered;  // 1: process only rows the streaming path reported as not covered, leave the others alone
+  int rows;            // set by launch_rows: a cluster walks rows cluster, cluster + clusters, ... below this
 };
 
 // Region sums of a non-negative per-id value (value(j) for local index j < len, 0 for ids outside the support):
@@ -166,16 +167,9 @@ __device__ int draw_token(RowCtx &c, double u, double rel_bound, double abs_boun
   return token;
 }
 
+// One row, start to finish, by the whole cluster.  Shared memory needs no particular content on entry.
 template <int kMode>
-__global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  RowSmem *s = reinterpret_cast<RowSmem *>(smem_raw);
-  RowCtx c = make_ctx(s, a.vocab);
-  const int row = blockIdx.x / c.nranks;
-  if (a.only_uncovered) {  // same answer in every CTA of the cluster, so the whole cluster leaves together
-    const int st = kMode == kModeSample ? a.status[row] : a.stats[row].status;
-    if (st != -8 && st != -9) return;  // -9: handed on by the batch path for wide nuclei (flat.cuh)
-  }
+__device__ __forceinline__ void row_body(const RowArgs &a, RowCtx &c, RowSmem *s, const int row) {
   const float *logits = a.logits + size_t(row) * a.logits_stride;
 
   bool used_tma;
@@ -279,6 +273,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
     for (int r = 0; r < c.nranks; ++r) lowest = fminf(lowest, all[r].f[1]);
   }
   int status = 0;
+  c.timed_out = (flags & 8) ? 1 : 0;
   if (flags & 8) status = -5;
   else if (flags & 1) status = -1;
   else if (flags & 4) status = -7;
@@ -388,8 +383,40 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
       a.stats[row] = st;
     }
   }
-  // no CTA may exit while a peer can still address its shared memory
-  c.cluster.sync();
+}
+
+// A cluster takes rows cluster, cluster + clusters, ...: one row per cluster when the launch has a cluster per row; a
+// small persistent grid when only the rows another path left over (status -8 / -9) are wanted, so that a launch with
+// nothing to do costs a few status reads instead of thousands of cluster launches.
+template <int kMode>
+__global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  RowSmem *s = reinterpret_cast<RowSmem *>(smem_raw);
+  RowCtx c = make_ctx(s, a.vocab);
+  const int clusters = int(gridDim.x) / c.nranks;
+  for (int row = int(blockIdx.x) / c.nranks; row < a.rows; row += clusters) {
+    if (a.only_uncovered) {  // same answer in every CTA of the cluster
+      const int st = kMode == kModeSample ? a.status[row] : a.stats[row].status;
+      if (st != -8 && st != -9) continue;  // -9: handed on by the batch path for wide nuclei (flat.cuh)
+    }
+    row_body<kMode>(a, c, s, row);
+    // no CTA may exit, or stage the next row, while a peer can still address its shared memory
+    c.cluster.sync();
+    if (c.timed_out) {  // a bounded wait expired: this cluster reports its remaining rows and stops
+      if (c.rank == 0 && c.tid == 0) {
+        for (int r = row + clusters; r < a.rows; r += clusters) {
+          if (kMode == kModeSample) {
+            if (a.only_uncovered && a.status[r] != -8 && a.status[r] != -9) continue;
+            a.tokens[r] = -1;
+            if (a.status) a.status[r] = -5;
+          } else if (!a.only_uncovered || a.stats[r].status == -8) {
+            a.stats[r].status = -5;
+          }
+        }
+      }
+      break;
+    }
+  }
 }
 
 }  // namespace ds41

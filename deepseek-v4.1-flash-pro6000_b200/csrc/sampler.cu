@@ -28,8 +28,12 @@ cudaError_t launch_rows(const RowArgs &a, int rows, cudaStream_t stream) {
     configured_device = dev;
   }
   const int cl = cluster_size_for(a.vocab);
+  RowArgs args = a;
+  args.rows = rows;
+  // left-over rows only: a persistent grid of two clusters per 8 SMs walks the status words
+  const int clusters = a.only_uncovered ? (rows < 74 ? rows : 74) : rows;
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(unsigned(rows) * cl);
+  cfg.gridDim = dim3(unsigned(clusters) * cl);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = sizeof(RowSmem);
   cfg.stream = stream;
@@ -37,7 +41,7 @@ cudaError_t launch_rows(const RowArgs &a, int rows, cudaStream_t stream) {
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = cl; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr; cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, row_kernel<kMode>, a);
+  return cudaLaunchKernelEx(&cfg, row_kernel<kMode>, args);
 }
 template cudaError_t launch_rows<kModeSample>(const RowArgs &, int, cudaStream_t);
 template cudaError_t launch_rows<kModeStats>(const RowArgs &, int, cudaStream_t);
