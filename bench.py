@@ -648,7 +648,7 @@ def main():
                 "e2e": {"value": units * e2e_steps / e2e_s, "unit": "sequences/s" if name.startswith("cfg3") else "tokens/s",
                         "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_s / e2e_steps * 1e3},
                 "gpu_launches": wl.launches_per_step * args.steps, "roofline": roof,
-                "launch": "one CUDA graph replay per step" if world == 1 else "eager launches (host checks the coverage flag every step)"}
+                "launch": "one CUDA graph replay per step" if world == 1 else "eager launches on one stream (kernels and NCCL collectives), no host synchronisation inside a step"}
         if same_as_single is not None:
             line["tokens_equal_single_gpu_path"] = same_as_single
         if getattr(wl, "exchange_note", None):
