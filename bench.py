@@ -161,10 +161,10 @@ class HeadSample:
         self.status = torch.empty(batch, dtype=torch.int32, device=device)
         self.tokens_host = torch.empty(batch, dtype=torch.int32).pin_memory()
         self.flag = torch.zeros(1, dtype=torch.int32, device=device)
-        # sampler scratch: with it, batches of 192 rows or more go through the batch path for wide nuclei first
+        # sampler scratch: with it, batches of 128 rows or more go through the batch path for wide nuclei first
         # (smaller batches of these flat logits go to the cluster kernel directly: the streaming path, which scratch
         # would also enable, only covers peaked distributions)
-        self.scratch = torch.empty(pkg.sample_scratch_bytes(batch, VOCAB), dtype=torch.uint8, device=device) if batch >= 192 else None
+        self.scratch = torch.empty(pkg.sample_scratch_bytes(batch, VOCAB), dtype=torch.uint8, device=device) if batch >= 128 else None
         self.units = batch
         self.h2d, self.d2h = batch * HIDDEN * 2, batch * 4
         # the two kernels that can dominate a step, each timed with its own event pair
@@ -181,15 +181,15 @@ class HeadSample:
         self.sharded = None
         self.exchange_note = None
         # own kernels per step: quantise, head, then the sampler call = flat_stats/hist/window/mass/resolve + the three
-        # predicated fall-through kernels (chunk, combine, row_kernel) for batches >= 192, else row_kernel alone
-        self.launches_per_step = 10 if batch >= 192 else 3
+        # predicated fall-through kernels (chunk, combine, row_kernel) for batches >= 128, else row_kernel alone
+        self.launches_per_step = 10 if batch >= 128 else 3
         if world > 1:
             self.sharded = import_module("ds41_b200.sharded").ShardedDecodeTail(pkg, device, batch, self.v0, self.vn,
                                                                               VOCAB, temperature, top_p, strategy)
             strategy = self.sharded.strategy  # "candidates" if the peer buffers could not be mapped
             self.exchange_note = self.sharded.exchange_error
             local_rows = -(-batch // world)
-            self.launches_per_step = (10 if local_rows >= 192 else 3) if strategy == "rows" else 6
+            self.launches_per_step = (10 if local_rows >= 128 else 3) if strategy == "rows" else 6
 
     def step(self, i, hidden=None, ev=None):
         pkg = self.pkg

@@ -5,6 +5,7 @@
 #include "flat.cuh"
 #include "host_error.h"
 #include <cmath>
+#include <cstdlib>
 
 namespace ds41 {
 
@@ -59,7 +60,16 @@ namespace {
 size_t streaming_bytes(int rows, int vocab) {
   return size_t(rows) * chunks_for(vocab) * sizeof(ChunkRecord) + ((size_t(rows) * 4 + 15) & ~size_t(15));
 }
-bool flat_shape(int rows, int vocab) { return rows >= kFlatMinRows && vocab >= kFlatMinVocab; }
+// DS41_FLAT_MIN_ROWS (read once) moves the batch size from which the batch path for wide nuclei is used
+int flat_min_rows() {
+  static const int value = [] {
+    const char *e = getenv("DS41_FLAT_MIN_ROWS");
+    const int v = e ? atoi(e) : 0;
+    return v >= 1 ? v : kFlatMinRows;
+  }();
+  return value;
+}
+bool flat_shape(int rows, int vocab) { return rows >= flat_min_rows() && vocab >= kFlatMinVocab; }
 }  // namespace
 
 extern "C" size_t ds41_b200_sample_scratch_bytes(int rows, int vocab) {

@@ -147,3 +147,57 @@ def test_rows_plan_covers_every_row_once():
             covered = [r for first, n in plan for r in range(first, first + n)]
             assert covered == list(range(rows))
             assert all(first == min(rows, r * per) for r, (first, _) in enumerate(plan))
+
+
+def rows_worker(rank, world, port, out):
+    """Row-sharded exchange on CPU: every rank samples its own rows (here: the oracle on full-vocabulary rows that the
+    other ranks' "head slices" were written into) and publishes; everyone must end with all tokens."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import __graft_entry__ as entry
+    import oracle_lib
+    entry.load_package()
+    sh = importlib.import_module("ds41_b200.sharded")
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    orc = oracle_lib.Oracle()
+    rows, vocab = 7, 2048          # 7 rows over 3 ranks: 3 + 3 + 1
+    x = orc.gen_logits(9, rows, vocab, sigma=2.0, zipf_s=1.1)
+    seeds, steps = np.arange(rows, dtype=np.uint64) + 11, np.arange(rows, dtype=np.uint64) * 3
+    want, wst = orc.sample_rows(x, 0.8, 0.9, seeds, steps, threads=2)
+    ex = sh.RowExchange.__new__(sh.RowExchange)     # no peer memory on CPU: only the host logic is under test
+    ex.world, ex.rank, ex.rows, ex.vocab, ex.group, ex.device = world, rank, rows, vocab, None, torch.device("cpu")
+    ex.rows_per_owner, plan = sh.rows_plan(rows, world)
+    ex.row0, ex.my_rows = plan[rank]
+    ex.packed = torch.full((2, ex.rows_per_owner), -1, dtype=torch.int32)
+    ex.everyone = torch.empty((world, 2, ex.rows_per_owner), dtype=torch.int32)
+    # the head's scatter, emulated: every rank contributes its vocabulary slice of every row to the row's owner
+    full = torch.zeros((ex.rows_per_owner, vocab))
+    pieces = [None] * world
+    v0, vn = sh.shard_plan(vocab, world)[rank]
+    dist.all_gather_object(pieces, (v0, vn, x[:, v0:v0 + vn].copy()))
+    for p0, pn, block in pieces:
+        full[:ex.my_rows, p0:p0 + pn] = torch.from_numpy(block[ex.row0:ex.row0 + ex.my_rows])
+    if ex.my_rows:
+        sl = slice(ex.row0, ex.row0 + ex.my_rows)
+        tok, st = orc.sample_rows(full[:ex.my_rows].numpy(), 0.8, 0.9, seeds[sl], steps[sl], threads=1)
+        ex.packed[0, :ex.my_rows] = torch.from_numpy(tok)
+        ex.packed[1, :ex.my_rows] = torch.from_numpy(st)
+    tokens, status = torch.empty(rows, dtype=torch.int32), torch.empty(rows, dtype=torch.int32)
+    ex.publish(tokens, status)
+    failures = []
+    if not (tokens.numpy() == want).all():
+        failures.append(f"rank {rank}: {tokens.numpy()} != {want}")
+    if not (status.numpy() == wst).all():
+        failures.append(f"rank {rank}: status {status.numpy()} != {wst}")
+    out[rank] = failures
+    dist.destroy_process_group()
+
+
+def test_three_rank_row_exchange_on_gloo():
+    world, port = 3, 31500 + os.getpid() % 2000
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(rows_worker, args=(world, port, out), nprocs=world, join=True)
+        assert len(out) == world
+        for rank in range(world):
+            assert out[rank] == [], out[rank]
