@@ -134,38 +134,60 @@ __device__ __forceinline__ FlatPartial row_extremes(const FlatArgs &a, int row) 
 
 struct FlatBins {  // binning of one row: bin = min(1023, int((max - y) * inv_w))
   float m, range, inv_w, c32, step;
+  float c_lo;  // log2(e)/T = c32 + c_lo to 2^-48
 };
 __device__ __forceinline__ FlatBins make_bins(const FlatPartial &e, double t) {
   FlatBins b;
   b.m = e.max;
-  b.c32 = float(1.4426950408889634074 / t);
+  const double c64 = 1.4426950408889634074 / t;
+  b.c32 = float(c64);
+  b.c_lo = float(c64 - double(b.c32));
   b.range = (e.max - e.min) * 1.0001f + 1e-30f;
   b.inv_w = float(kFlatBins) / b.range;
   b.step = b.range / float(kFlatBins) * b.c32;  // bin width in units of the exponent of 2
   return b;
 }
 
-// Fixed-point scale of the histogram masses: an id of bin k adds round(kQ * w / 2^-(k*step)), a number in
-// (0.97 kQ, kQ]; a quarter row holds at most 32768 ids, so a 32-bit shared-memory word cannot wrap (32768 * 2^17 =
-// 2^32 is excluded by capping the addend at kQ - 1), and one integer atomic per id accumulates exactly.
-constexpr float kQ = 131072.f;
-constexpr double kQInv = 1.0 / 131072.0;
+// Histogram mass of an id of bin k, in fixed point relative to the weight at the bin's near edge:
+// Q = round(2^24 * w / 2^-(k*step)), w = 2^-X, X = (m - y) * log2(e)/T.  X is formed in double-float (the difference by
+// TwoSum, the product with the constant split in two floats: good to 3 * 2^-47 relative), the exponent k*step - X of
+// the quotient with one fused multiply-add from its head (|quotient exponent| <= step, so the rounding there is below
+// 2^-29 absolute), ex2.approx is within 2^-22, the product by 2^24 within 2^-24 and the rounding to an integer within
+// 2^-25 of a value above 0.94 * 2^24.  Relative error of Q * 2^-24 * 2^-(k*step) as a weight: below 2.9e-7 (test:
+// against long double); integer accumulation adds nothing.  The two halves of Q go to two 32-bit shared-memory words
+// (a CTA sees at most 32768 ids: 32768 * 65535 and 32768 * 512 both fit), i.e. two integer atomics per id.
+constexpr double kHistRel = 3.2e-7;  // 2.9e-7 rounded up
+__device__ __forceinline__ unsigned fixed_weight(float y, const FlatBins &b, int *bin) {
+  const float s = __fsub_rn(b.m, y);
+  const float bb = __fsub_rn(s, b.m);
+  const float ed = __fadd_rn(__fsub_rn(b.m, __fsub_rn(s, bb)), __fsub_rn(-y, bb));  // m - y = s + ed exactly
+  const float p = __fmul_rn(s, b.c32);
+  const float pe = __fmaf_rn(s, b.c32, -p);                                         // s * c32 = p + pe exactly
+  const float q = __fmaf_rn(s, b.c_lo, __fmaf_rn(ed, b.c32, pe));                   // X = p + q
+  const int k = min(kFlatBins - 1, int(__fmul_rn(s, b.inv_w)));
+  *bin = k;
+  const float r = __fsub_rn(__fmaf_rn(float(k), b.step, -p), q);                    // k*step - X, in [-step, 0] but for the last bin
+  // (the bin index comes from a differently rounded quotient than the edge k*step, so r can exceed 0 by a few 1e-5:
+  // the quotient is allowed above 1; the cap only guards the 32-bit sums against a wild value)
+  return min(33554431u, __float2uint_rn(__fmul_rn(16777216.f, ex2_approx(r))));
+}
 
 __global__ void __launch_bounds__(kFT) flat_hist_kernel(FlatArgs a) {
-  __shared__ unsigned qmass[kFlatBins];
+  __shared__ unsigned lo16[kFlatBins], hi8[kFlatBins];
   const int row = blockIdx.x / a.chunks, chunk = blockIdx.x % a.chunks;
   const FlatPartial ext = row_extremes(a, row);
   if (ext.flags || !(ext.min < ext.max)) return;  // the window kernel reports the row
   const FlatBins b = make_bins(ext, a.t);
-  for (int j = threadIdx.x; j < kFlatBins; j += kFT) qmass[j] = 0u;
+  for (int j = threadIdx.x; j < kFlatBins; j += kFT) { lo16[j] = 0u; hi8[j] = 0u; }
   __syncthreads();
   int begin, end;
   quarter(a, chunk, &begin, &end);
   const float *x = a.logits + size_t(row) * a.stride;
   auto take = [&](float y) {
-    const float d = b.m - y;
-    const int k = min(kFlatBins - 1, int(d * b.inv_w));
-    atomicAdd(&qmass[k], min(131071u, __float2uint_rn(kQ * ex2_approx(fmaf(float(k), b.step, -(d * b.c32))))));
+    int k;
+    const unsigned q = fixed_weight(y, b, &k);
+    atomicAdd(&lo16[k], q & 0xffffu);
+    atomicAdd(&hi8[k], q >> 16);
   };
   const int vec_end = begin + ((end - begin) & ~3);
   for (int i = begin + 4 * threadIdx.x; i < vec_end; i += 4 * kFT) {
@@ -175,8 +197,8 @@ __global__ void __launch_bounds__(kFT) flat_hist_kernel(FlatArgs a) {
   for (int i = vec_end + threadIdx.x; i < end; i += kFT) take(__ldg(x + i));
   __syncthreads();
   for (int j = threadIdx.x; j < kFlatBins; j += kFT) {
-    const unsigned q = qmass[j];
-    if (q) atomicAdd(&a.s.hmass[size_t(row) * kFlatBins + j], (unsigned long long)q);
+    const unsigned long long q = ((unsigned long long)hi8[j] << 16) + lo16[j];
+    if (q) atomicAdd(&a.s.hmass[size_t(row) * kFlatBins + j], q);
   }
 }
 
@@ -197,26 +219,20 @@ __global__ void __launch_bounds__(kFT) flat_window_kernel(FlatArgs a) {
     return;
   }
   const FlatBins b = make_bins(ext, a.t);
-  // ids of a bin, bracketed from its fixed-point mass (every id adds between 0.97 kQ and kQ): enough to tell a wide
-  // nucleus from a small one and whether the window fits the list; the exact counts come from the FP64 pass
+  // ids of a bin, bracketed from its fixed-point mass (every id adds between 0.94 * 2^24 and 2^24): enough to tell a
+  // wide nucleus from a small one and whether the window fits the list; the exact counts come from the FP64 pass
   int cnt_lo[2] = {0, 0}, cnt_hi[2] = {0, 0};
-  double lo[2] = {0, 0}, hi[2] = {0, 0};
+  double lo[2] = {0, 0}, hi[2] = {0, 0}, mid[2] = {0, 0};
   if (ext.min < ext.max) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       const int k = 2 * threadIdx.x + i;
       const unsigned long long q = a.s.hmass[size_t(row) * kFlatBins + k];
-      // Error of the measured mass of a bin, per id: the FP32 argument carries three roundings relative to
-      // |x| <= (k+1)*step plus one of the product k*step (together < 2.8 |x| * 2^-24 in the weight; 5.6 allowed),
-      // ex2.approx is within 2^-22, the product by kQ within 2^-24, the rounding to an integer (and the cap at
-      // kQ - 1) within 2^-17 of a value near kQ = 128 * 2^-24; the edge weight below is an FP64 exp2 of the same
-      // FP32 product.  Integer accumulation adds nothing.
-      const double x_far = (double(k) + 1.0) * double(b.step) * 1.0001;
-      const double e = (5.6 * x_far + 4.0 + 1.0 + 160.0 + 4.0) * 5.9604644775390625e-8;
-      const double mass = double(q) * kQInv * exp2(-double(float(k) * b.step));
-      lo[i] = mass * (1.0 - e); hi[i] = mass * (1.0 + e);
-      cnt_lo[i] = int(q >> 17);                                   // every id adds at most kQ
-      cnt_hi[i] = int((double(q) * kQInv) / 0.97) + (q ? 1 : 0);  // and at least 0.97 kQ (bin width << 0.04 in exponent)
+      const double mass = double(q) * 5.9604644775390625e-8 * exp2(-double(k) * double(b.step));
+      mid[i] = mass;
+      lo[i] = mass * (1.0 - kHistRel); hi[i] = mass * (1.0 + kHistRel);
+      cnt_lo[i] = int(double(q) * 5.9604644775390625e-8 / 1.001);                // every id adds at most 1.001 * 2^24
+      cnt_hi[i] = int((double(q) * 5.9604644775390625e-8) / 0.94) + (q ? 1 : 0);  // and at least 0.94 * 2^24 (step <= 0.08)
     }
   }
   const double lo0 = flat_prefix2(red, lo[0], lo[1]), hi0 = flat_prefix2(red, hi[0], hi[1]);
@@ -241,36 +257,26 @@ __global__ void __launch_bounds__(kFT) flat_window_kernel(FlatArgs a) {
   through = flat_sum(red, through);
   inside = flat_sum(red, inside);
   // this path's case: a window exists, the nucleus is wide (a small one is the other paths' case), the window fits
-  // the list, and the bins are narrow enough for the count bracket above (step <= 0.04: any row whose range times
-  // 1.44/T is below 41)
-  const bool ok = found && through > kFlatMinNucleus && inside <= kFlatList && b.step <= 0.04f;
+  // the list, and the bins are narrow enough for the count bracket above (step <= 0.08: any row whose range times
+  // 1.44/T is below 82)
+  const bool ok = found && through > kFlatMinNucleus && inside <= kFlatList && b.step <= 0.08f;
+  // mass of the ids beyond the window, as the histogram has it: their only use is as part of the normaliser
+  double beyond = 0;
+  if (found) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      if (2 * threadIdx.x + i > w1) beyond += mid[i];
+  }
+  beyond = flat_sum(red, beyond);
   if (threadIdx.x == 0) {
-    info.applicable = ok ? 1 : 0; info.w0 = w0; info.w1 = w1;
+    info.applicable = ok ? 1 : 0; info.w0 = w0; info.w1 = w1; info.tail = beyond;
     a.s.info[row] = info;
     if (!ok) { a.tokens[row] = -1; a.status[row] = -8; }
   }
 }
 
-// Weight of an id BEYOND the window (it only enters the normaliser, and all such ids together hold less than
-// 1 - top_p of it) in FP32-class arithmetic: 2^-X with X = (m - y) * log2(e)/T formed in double-float (the difference
-// by TwoSum, the product with the constant split in two floats: X is good to 3 * 2^-47 relative), split X = n + f with
-// |f| <= 1/2, ex2.approx(-f) (within 2^-22) times the exact power 2^-n.  Relative error of the result below 2.7e-7
-// (test: against long double on 10^7 arguments); weights below 2^-126 come out as 0.
-struct TailExp { float m, c_hi, c_lo; };
-__device__ __forceinline__ float tail_weight(float y, const TailExp &k) {
-  const float s = __fsub_rn(k.m, y);
-  const float bb = __fsub_rn(s, k.m);
-  const float ed = __fadd_rn(__fsub_rn(k.m, __fsub_rn(s, bb)), __fsub_rn(-y, bb));  // m - y = s + ed exactly
-  const float p = __fmul_rn(s, k.c_hi);
-  const float pe = __fmaf_rn(s, k.c_hi, -p);                                        // s * c_hi = p + pe exactly
-  const float q = __fmaf_rn(s, k.c_lo, __fmaf_rn(ed, k.c_hi, pe));
-  const float n = rintf(p);
-  const float f = __fadd_rn(__fsub_rn(p, n), q);
-  const int ni = int(n);
-  return ni > 126 ? 0.f : __fmul_rn(ex2_approx(-f), __int_as_float((127 - ni) << 23));
-}
-constexpr double kTailRel = 4.5e-7;  // per-term 2.7e-7 + compensated FP32 summation 1.2e-7, rounded up
-
+// The ids beyond the window only enter the normaliser, hold less than 1 - top_p of it, and the histogram pass already
+// has their mass to kHistRel: the FP64 pass skips them.
 __global__ void __launch_bounds__(kFT, 2) flat_mass_kernel(FlatArgs a) {
   // per-warp queue of the ids that need an FP64 weight (before or inside the window): position in the sub-region
   __shared__ float queue_y[kFW][256];
@@ -283,8 +289,6 @@ __global__ void __launch_bounds__(kFT, 2) flat_mass_kernel(FlatArgs a) {
   const FlatBins b = make_bins(ext, a.t);
   const float edge0 = float(info.w0), edge1 = info.w1 >= kFlatBins - 1 ? CUDART_INF_F : float(info.w1 + 1);
   const double inv_t = 1.0 / a.t, m64 = double(info.max);
-  const double c64 = 1.4426950408889634074 / a.t;
-  const TailExp tail{info.max, float(c64), float(c64 - double(float(c64)))};
   const float *x = a.logits + size_t(row) * a.stride;
   const int subs_per_warp = kFlatSubs / a.chunks / kFW;  // 2 or 1
 #pragma unroll 1
@@ -293,7 +297,6 @@ __global__ void __launch_bounds__(kFT, 2) flat_mass_kernel(FlatArgs a) {
     const int base = sub * kFlatSub;
     double z = 0, sure_mass = 0;
     int sure_count = 0;
-    float tail_sum = 0.f, tail_comp = 0.f;  // compensated FP32 sum of the lane's tail weights
     int head = 0, count = 0;                // queue state, warp-uniform
     // FP64 weights of up to 32 queued ids (lane i takes entry head + i)
     auto drain = [&](int take) {
@@ -347,7 +350,7 @@ __global__ void __launch_bounds__(kFT, 2) flat_mass_kernel(FlatArgs a) {
       const float4 nxt = j + 1 < kFlatSub / 128 ? fetch(j + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
       const float ys4[4] = {cur.x, cur.y, cur.z, cur.w};
       const int at0 = (j * 32 + lane) * 4;
-      // ids up to the window's far edge go to the FP64 queue, the others are tail; the lane's (up to four) queue
+      // ids up to the window's far edge go to the FP64 queue, the others are skipped; the lane's (up to four) queue
       // entries are placed with one warp-wide prefix of the lanes' counts (three votes on the bits of the count)
       int mine = 0;
       bool near[4];
@@ -357,12 +360,6 @@ __global__ void __launch_bounds__(kFT, 2) flat_mass_kernel(FlatArgs a) {
         const bool valid = base + at0 + q4 < a.vocab;
         near[q4] = valid && (b.m - y) * b.inv_w < edge1;
         mine += near[q4] ? 1 : 0;
-        if (valid && !near[q4]) {
-          const float w = tail_weight(y, tail);
-          const float t1 = __fsub_rn(w, tail_comp), t2 = __fadd_rn(tail_sum, t1);
-          tail_comp = __fsub_rn(__fsub_rn(t2, tail_sum), t1);
-          tail_sum = t2;
-        }
       }
       const unsigned below = (1u << lane) - 1u;
       const unsigned v1 = __ballot_sync(0xffffffffu, mine & 1), v2 = __ballot_sync(0xffffffffu, mine & 2),
@@ -382,19 +379,16 @@ __global__ void __launch_bounds__(kFT, 2) flat_mass_kernel(FlatArgs a) {
       cur = nxt;
     }
     if (count > 0) drain(count);
-    double tail64 = double(tail_sum) - double(tail_comp);
 #pragma unroll
     for (int o = 16; o; o >>= 1) {
       z += __shfl_xor_sync(0xffffffffu, z, o);
       sure_mass += __shfl_xor_sync(0xffffffffu, sure_mass, o);
-      tail64 += __shfl_xor_sync(0xffffffffu, tail64, o);
     }
     sure_count = __reduce_add_sync(0xffffffffu, sure_count);
     if (lane == 0) {
-      a.s.subz[size_t(row) * kFlatSubs + sub] = z + tail64;
+      a.s.subz[size_t(row) * kFlatSubs + sub] = z;
       a.s.subsure[size_t(row) * kFlatSubs + sub] = sure_mass;
       a.s.subcnt[size_t(row) * kFlatSubs + sub] = sure_count;
-      a.s.subtail[size_t(row) * kFlatSubs + sub] = tail64;
     }
   }
 }
@@ -415,17 +409,16 @@ __global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
   const float *x = a.logits + size_t(row) * a.stride;
   const int listed = a.s.lcount[row * 4];
   // normaliser, mass and count before the window: fixed order (sub-regions across threads, then the block tree)
-  double z = 0, mass_before = 0, tail = 0;
+  double z = 0, mass_before = 0;
+  const double tail = info.tail;  // ids beyond the window, from the histogram pass (relative error kHistRel)
   int n_before = 0;
   if (tid < kFlatSubs) {
     z = a.s.subz[size_t(row) * kFlatSubs + tid];
-    tail = a.s.subtail[size_t(row) * kFlatSubs + tid];
     mass_before = a.s.subsure[size_t(row) * kFlatSubs + tid];
     n_before = a.s.subcnt[size_t(row) * kFlatSubs + tid];
     ksum[tid] = mass_before;
   }
-  z = flat_sum(red, z);
-  tail = flat_sum(red, tail);
+  z = flat_sum(red, z) + tail;
   mass_before = flat_sum(red, mass_before);
   n_before = flat_sum(red, n_before);
   bool ok = listed >= 1 && listed <= kFlatList;
@@ -483,13 +476,13 @@ __global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
   }
   const double through0 = mass_before + flat_prefix2(red, e[0], e[1]), through1 = through0 + e[1];
   const double rel = 2.0 * (double(a.vocab) + 256.0) * kU;
-  // Two attempts at the crossing.  First with the normaliser as the mass pass left it: the ids beyond the window entered
-  // it with FP32-class weights, so their share of z carries a relative error kTailRel.  If the crossing falls inside
+  // Two attempts at the crossing.  First with the normaliser as the earlier passes left it: the ids beyond the window
+  // enter it with the histogram's FP32-class masses, so their share of z carries a relative error kHistRel.  If the crossing falls inside
   // that wider bound (about one row in a hundred), this CTA recomputes the tail of its row with FP64 weights and
   // decides again with the FP64 bound alone.
   const FlatBins b = make_bins(FlatPartial{info.max, info.min, info.argmax, 0}, a.t);
   const float edge1 = info.w1 >= kFlatBins - 1 ? CUDART_INF_F : float(info.w1 + 1);
-  double tail_abs = a.top_p * (kTailRel * tail + 1e-30);
+  double tail_abs = a.top_p * (kHistRel * tail + 1e-30);
   int pos = 0x7fffffff;
   for (int attempt = 0; attempt < 2; ++attempt) {
     const double target_p = a.top_p * z, lo = target_p * (1.0 - rel) - tail_abs, hi = target_p * (1.0 + rel) + tail_abs;
@@ -621,17 +614,29 @@ __global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
   (void)lane;
 }
 
-__global__ void tail_probe_kernel(const float *y, TailExp k, float *out, int n) {
+__global__ void hist_probe_kernel(const float *y, FlatBins b, double *out, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) out[i] = tail_weight(y[i], k);
+  if (i >= n) return;
+  int k;
+  const unsigned q = fixed_weight(y[i], b, &k);
+  out[i] = double(q) * 5.9604644775390625e-8 * exp2(-double(k) * double(b.step));
 }
 
 }  // namespace
 
-cudaError_t launch_tail_probe(const float *y, float m, double t, float *out, int n, cudaStream_t stream) {
-  const double c64 = 1.4426950408889634074 / t;
-  const TailExp k{m, float(c64), float(c64 - double(float(c64)))};
-  tail_probe_kernel<<<(n + 255) / 256, 256, 0, stream>>>(y, k, out, n);
+cudaError_t launch_hist_probe(const float *y, float max_logit, float min_logit, double t, double *out, int n,
+                              cudaStream_t stream) {
+  FlatBins b;
+  {  // make_bins is device code; the same arithmetic on the host (FP32 operations are IEEE on both sides)
+    const double c64 = 1.4426950408889634074 / t;
+    b.m = max_logit;
+    b.c32 = float(c64);
+    b.c_lo = float(c64 - double(b.c32));
+    b.range = (max_logit - min_logit) * 1.0001f + 1e-30f;
+    b.inv_w = float(kFlatBins) / b.range;
+    b.step = b.range / float(kFlatBins) * b.c32;
+  }
+  hist_probe_kernel<<<(n + 255) / 256, 256, 0, stream>>>(y, b, out, n);
   return cudaGetLastError();
 }
 
@@ -647,7 +652,7 @@ cudaError_t launch_flat(FlatArgs a, void *scratch, cudaStream_t stream) {
   unsigned char *p = static_cast<unsigned char *>(scratch);
   const size_t rows = size_t(a.rows);
   a.s.hmass = reinterpret_cast<unsigned long long *>(p); p += rows * kFlatBins * sizeof(unsigned long long);
-  a.s.subtail = reinterpret_cast<double *>(p); p += rows * kFlatBins * sizeof(unsigned);  // rows * kFlatSubs doubles fit
+  p += rows * kFlatBins * sizeof(unsigned);  // (spare)
   a.s.lcount = reinterpret_cast<int *>(p); p += rows * 4 * sizeof(int);
   const size_t zeroed = size_t(p - static_cast<unsigned char *>(scratch));
   a.s.lkeys = reinterpret_cast<unsigned long long *>(p); p += rows * kFlatList * sizeof(unsigned long long);

@@ -20,13 +20,16 @@ constexpr int kFlatMinVocab = 16384;
 constexpr int kNeedsCluster = -9;
 
 struct FlatPartial { float max, min; int argmax, flags; };
-struct FlatInfo { float max, min; int argmax, applicable, w0, w1, pad0, pad1; };
+struct FlatInfo {
+  float max, min;
+  int argmax, applicable, w0, w1;
+  double tail;  // mass of the ids beyond the window as the histogram pass has it
+};
 struct FlatScratch {
   FlatPartial *partial;        // [rows][kFlatMaxChunks]
-  double *subtail;             // [rows][kFlatSubs]: FP32-class part of subz (ids beyond the window)
   unsigned long long *hmass;   // [rows][kFlatBins], fixed point relative to the bin's near edge
   FlatInfo *info;              // [rows]
-  double *subz, *subsure;      // [rows][kFlatSubs]: normaliser part, mass of the ids before the window
+  double *subz, *subsure;      // [rows][kFlatSubs]: FP64 mass of the ids up to the window's far edge / before the window
   int *subcnt;                 // [rows][kFlatSubs]
   int *lcount;                 // [rows][4]: window list length, "a 32-bit mass may have wrapped" flag
   unsigned long long *lkeys;   // [rows][kFlatList]

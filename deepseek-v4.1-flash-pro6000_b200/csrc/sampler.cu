@@ -150,11 +150,13 @@ __global__ void exp_probe_kernel(const double *x, double *out, int n) {
 }
 }  // namespace ds41
 
-namespace ds41 { cudaError_t launch_tail_probe(const float *y, float m, double t, float *out, int n, cudaStream_t stream); }
-extern "C" int ds41_b200_test_tail_weight(const float *y, float max_logit, double temperature, float *out, int n,
-                                          cudaStream_t stream) {
-  if (!y || !out || n < 1 || !(temperature > 0)) return invalid("tail probe arguments");
-  return int(ds41::launch_tail_probe(y, max_logit, temperature, out, n, stream));
+namespace ds41 {
+cudaError_t launch_hist_probe(const float *y, float max_logit, float min_logit, double t, double *out, int n, cudaStream_t stream);
+}
+extern "C" int ds41_b200_test_hist_weight(const float *y, float max_logit, float min_logit, double temperature,
+                                          double *out, int n, cudaStream_t stream) {
+  if (!y || !out || n < 1 || !(temperature > 0) || !(min_logit < max_logit)) return invalid("histogram probe arguments");
+  return int(ds41::launch_hist_probe(y, max_logit, min_logit, temperature, out, n, stream));
 }
 
 extern "C" int ds41_b200_test_exp_nonpos(const double *x, double *out, int n, cudaStream_t stream) {

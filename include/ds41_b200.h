@@ -212,10 +212,11 @@ int ds41_b200_peer_free(void *ptr);
  * out[i] = the samplers' own exp(x[i]) for x <= 0 (device pointers), so that its error can be measured against a
  * reference exponential.  No counterpart in the reference. */
 int ds41_b200_test_exp_nonpos(const double *x, double *out, int n, cudaStream_t stream);
-/* out[i] = the batch sampler's FP32-class weight exp((y[i] - max_logit) / temperature) of an id beyond the top-p
- * window (y[i] <= max_logit; device pointers), for the test of its stated error bound. */
-int ds41_b200_test_tail_weight(const float *y, float max_logit, double temperature, float *out, int n,
-                               cudaStream_t stream);
+/* out[i] = the weight exp((y[i] - max_logit) / temperature) as the batch sampler's histogram pass measures it (fixed
+ * point relative to the near edge of the id's bin, bins over [min_logit, max_logit]; device pointers), for the test of
+ * its stated error bound. */
+int ds41_b200_test_hist_weight(const float *y, float max_logit, float min_logit, double temperature, double *out,
+                               int n, cudaStream_t stream);
 
 #ifdef __cplusplus
 }
