@@ -79,8 +79,12 @@ int ds41_fuse_head_fp8(const void *x_bf16, const void *w_e4m3, const float *w_sc
  *   argmax(logits) for temperature 0   (engine/src/sampling.cpp:133-139; server.cpp:623-625)
  * Row r draws with the Philox address (seeds[r], steps[r], slot, purpose) (spark_rng.h:23-36).
  * The temperature floor max(T,1e-5) of the adapter is applied here (engine/src/sampling.cpp:209-210).
- * top_k, the three penalties and the bitmask have no counterpart in the reference; their rule is stated in
- * DESIGN.md and implemented identically by the CPU oracle. */
+ * top_k, the three penalties and the bitmask have no counterpart in the reference.  Their rule: count[id] =
+ * occurrences of id in the row's history; for count > 0, in FP32 with every operation rounded separately,
+ * y = x > 0 ? x / repetition : x * repetition, then y -= (presence + frequency * float(count)) (a non-finite result
+ * rejects the row); ids whose mask bit is 0 are excluded (no id left rejects the row); top_k keeps the first k
+ * remaining ids in the order (y descending, id ascending); the reference rule then runs on the survivors.  The CPU
+ * oracle of the tests implements the same rule. */
 typedef struct ds41_b200_sample_args {
   uint32_t struct_bytes;      /* sizeof(ds41_b200_sample_args): ABI check */
   int32_t rows, vocab;        /* 1 <= vocab <= DS41_B200_MAX_VOCAB */
