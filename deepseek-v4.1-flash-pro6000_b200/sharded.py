@@ -260,8 +260,13 @@ class RowExchange:
             dist.all_gather_into_tensor(self.everyone.view(-1), self.packed.view(-1), group=self.group)
         else:
             self.everyone[0] = self.packed
-        tokens.copy_(self.everyone[:, 0, :].reshape(-1)[: self.rows])
-        status.copy_(self.everyone[:, 1, :].reshape(-1)[: self.rows])
+        if self.rows == self.world * self.rows_per_owner and tokens.is_contiguous() and status.is_contiguous():
+            # one strided copy each, no temporary
+            tokens.view(self.world, self.rows_per_owner).copy_(self.everyone[:, 0, :])
+            status.view(self.world, self.rows_per_owner).copy_(self.everyone[:, 1, :])
+        else:
+            tokens.copy_(self.everyone[:, 0, :].reshape(-1)[: self.rows])
+            status.copy_(self.everyone[:, 1, :].reshape(-1)[: self.rows])
 
     def close(self):
         for p in self._opened:

@@ -149,7 +149,7 @@ def test_rows_plan_covers_every_row_once():
             assert all(first == min(rows, r * per) for r, (first, _) in enumerate(plan))
 
 
-def rows_worker(rank, world, port, out):
+def rows_worker(rank, world, port, out, rows=7):
     """Row-sharded exchange on CPU: every rank samples its own rows (here: the oracle on full-vocabulary rows that the
     other ranks' "head slices" were written into) and publishes; everyone must end with all tokens."""
     sys.path.insert(0, ROOT)
@@ -160,7 +160,7 @@ def rows_worker(rank, world, port, out):
     sh = importlib.import_module("ds41_b200.sharded")
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     orc = oracle_lib.Oracle()
-    rows, vocab = 7, 2048          # 7 rows over 3 ranks: 3 + 3 + 1
+    vocab = 2048                   # 7 rows over 3 ranks: 3 + 3 + 1 (ragged); 6 rows: 2 + 2 + 2 (single strided copy)
     x = orc.gen_logits(9, rows, vocab, sigma=2.0, zipf_s=1.1)
     seeds, steps = np.arange(rows, dtype=np.uint64) + 11, np.arange(rows, dtype=np.uint64) * 3
     want, wst = orc.sample_rows(x, 0.8, 0.9, seeds, steps, threads=2)
@@ -193,11 +193,12 @@ def rows_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_three_rank_row_exchange_on_gloo():
-    world, port = 3, 31500 + os.getpid() % 2000
+@pytest.mark.parametrize("rows", [7, 6])
+def test_three_rank_row_exchange_on_gloo(rows):
+    world, port = 3, 31500 + (os.getpid() + rows * 37) % 2000
     with mp.Manager() as mgr:
         out = mgr.dict()
-        mp.spawn(rows_worker, args=(world, port, out), nprocs=world, join=True)
+        mp.spawn(rows_worker, args=(world, port, out, rows), nprocs=world, join=True)
         assert len(out) == world
         for rank in range(world):
             assert out[rank] == [], out[rank]
