@@ -127,3 +127,32 @@ def test_histogram_weight_error_bound(pkg):
         rel = np.abs(got[ok] - want[ok]) / want[ok]
         worst = max(worst, float(rel.max()))
     assert worst < 2.9e-7, worst
+
+
+@pytest.mark.parametrize("case", range(8))
+def test_random_shapes_agree_with_cluster_kernel(pkg, case):
+    """Randomised distributions (scale, offset, tails), temperatures and top-p: the batch path and the cluster kernel are
+    independent implementations of the same certified rule, so wherever both certify they must give the same token."""
+    rng = np.random.default_rng(100 + case)
+    rows = 256
+    g = torch.Generator(device="cuda").manual_seed(200 + case)
+    sigma = float(rng.choice([0.3, 0.8, 1.28, 2.0, 3.5]))
+    offset = float(rng.choice([0.0, -7.25, 41.5, 300.0, -1000.0]))
+    x = sigma * torch.randn(rows, V, device="cuda", generator=g)
+    if case % 3 == 1:   # heavier tails: product of two normals
+        x = x * torch.randn(rows, V, device="cuda", generator=g).abs().clamp_(max=4.0)
+    if case % 3 == 2:   # a few towering ids on top of the flat bulk
+        idx = torch.randint(0, V, (rows, 5), device="cuda", generator=g)
+        x.scatter_add_(1, idx, torch.full((rows, 5), 4.0 * sigma, device="cuda"))
+    x = (x + offset).contiguous()
+    t = float(rng.choice([0.3, 0.6, 0.8, 1.0, 1.5]))
+    top = float(rng.choice([0.5, 0.8, 0.9, 0.95, 0.99, 0.999]))
+    seeds, steps = np.arange(rows) * 3 + case, np.arange(rows) + 50 * case
+    tok, st, scratch = sample(pkg, x, t, top, seeds, steps, slot=case % 6, purpose=case % 4)
+    ref, rst = pkg.sample_logits(x, t, top, u64(seeds), u64(steps), slot=case % 6, purpose=case % 4, scratch=None)
+    torch.cuda.synchronize()
+    ref, rst = ref.cpu().numpy(), rst.cpu().numpy()
+    assert (st >= 0).all() and (rst >= 0).all(), (st[st < 0], rst[rst < 0])
+    both = (st == 0) & (rst == 0)
+    assert both.mean() > 0.99
+    assert (tok[both] == ref[both]).all(), (sigma, offset, t, top, np.flatnonzero(tok != ref))
