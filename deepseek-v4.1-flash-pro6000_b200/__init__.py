@@ -54,6 +54,11 @@ class VerifyArgs(C.Structure):
                 ("scratch_bytes", C.c_size_t)]
 
 
+class ScoreArgs(C.Structure):
+    _fields_ = [("struct_bytes", _u32), ("rows", _i32), ("vocab", _i32), ("logits", _P), ("logits_stride", _i64),
+                ("top_n", _i32), ("logsumexp", _P), ("top1", _P), ("top_ids", _P), ("top_logprob", _P), ("status", _P)]
+
+
 _lib = None
 
 
@@ -84,6 +89,7 @@ def lib():
         L.ds41_fuse_head_fp8.argtypes = [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, _P, C.c_size_t, _P, _P]
         L.ds41_b200_verify_scratch_bytes.restype = C.c_size_t
         L.ds41_b200_verify_scratch_bytes.argtypes = [C.c_int, C.c_int]
+        L.ds41_b200_score_logits.argtypes = [C.POINTER(ScoreArgs), _P]
         _lib = L
     return _lib
 
@@ -268,6 +274,26 @@ def head_fp8(a, a_scale, w, w_scale, logits=None, error_flag=None):
                                         error_flag.data_ptr() if error_flag is not None else None, _stream()),
                "ds41_b200_head_fp8")
     return logits
+
+
+def score_logits(logits, top_n=0):
+    """log_normalizer + top_order of the reference's score / logprobs events (engine/src/server.cpp:178-183,730-737)
+    on device logits [rows, vocab].  Returns (logsumexp f64 [rows], top1 i32 [rows], top_ids i32 [rows, top_n],
+    top_logprob f64 [rows, top_n], status i32 [rows])."""
+    if logits.dim() != 2 or logits.stride(1) != 1 or not logits.is_cuda or logits.dtype != torch.float32:
+        raise ValueError("logits must be a CUDA fp32 [rows, vocab] tensor with unit inner stride")
+    rows, vocab = logits.shape
+    dev = logits.device
+    lse = torch.empty(rows, dtype=torch.float64, device=dev)
+    top1 = torch.empty(rows, dtype=torch.int32, device=dev)
+    ids = torch.empty((rows, top_n), dtype=torch.int32, device=dev)
+    lp = torch.empty((rows, top_n), dtype=torch.float64, device=dev)
+    status = torch.empty(rows, dtype=torch.int32, device=dev)
+    a = ScoreArgs(C.sizeof(ScoreArgs), rows, vocab, logits.data_ptr(), logits.stride(0), top_n, lse.data_ptr(),
+                  top1.data_ptr(), ids.data_ptr() if top_n else None, lp.data_ptr() if top_n else None, status.data_ptr())
+    with torch.cuda.device(dev):
+        _check(lib().ds41_b200_score_logits(C.byref(a), _stream()), "ds41_b200_score_logits")
+    return lse, top1, ids, lp, status
 
 
 def fuse_head_fp8_workspace_bytes(M, K):

@@ -212,6 +212,28 @@ int ds41_b200_peer_open(const void *handle, void **ptr);
 int ds41_b200_peer_close(void *ptr);
 int ds41_b200_peer_free(void *ptr);
 
+/* ---- score reporting: log-normaliser and top-N log-probabilities of device logits ------------------------------------
+ * Replaces the host passes of the reference's score / logprobs events: log_normalizer (engine/src/server.cpp:178-183),
+ * top_order (:730-737: the first n ids in the order logit descending, id ascending) and `double(l[t]) - normalizer`
+ * (:450-461, :603-612).  top ids and top1 are exact; logsumexp and the log-probabilities agree with the reference's
+ * sequential FP64 sum to a few units in the last place (relative 1e-13 is the tested tolerance).  Rows with a
+ * non-finite logit get status DS41_B200_ROW_NONFINITE, NaN values and ids -1.  The logits_sha256 fingerprint of the
+ * same event is not computed here. */
+#define DS41_B200_SCORE_MAX_TOP 32
+typedef struct ds41_b200_score_args {
+  uint32_t struct_bytes;
+  int32_t rows, vocab;
+  const float *logits;    /* [rows, logits_stride] fp32 */
+  int64_t logits_stride;
+  int32_t top_n;          /* 0..DS41_B200_SCORE_MAX_TOP */
+  double *logsumexp;      /* [rows] out */
+  int32_t *top1;          /* [rows] out: first maximum; may be NULL */
+  int32_t *top_ids;       /* [rows, top_n] out */
+  double *top_logprob;    /* [rows, top_n] out */
+  int32_t *status;        /* [rows] out */
+} ds41_b200_score_args;
+int ds41_b200_score_logits(const ds41_b200_score_args *args, cudaStream_t stream);
+
 /* ---- test hook ---------------------------------------------------------------------------------------------------
  * out[i] = the samplers' own exp(x[i]) for x <= 0 (device pointers), so that its error can be measured against a
  * reference exponential.  No counterpart in the reference. */

@@ -409,6 +409,33 @@ int oracle_argmax(const float *x, int n, int32_t *out) {
   ORACLE_END
 }
 
+// Score reporting of one row (engine/src/server.cpp:178-183 log_normalizer: max, then the sequential FP64 sum of
+// exp(double(v) - max), result max + log(sum); :730-737 top_order: the first n ids in the order value descending, id
+// ascending; :450-461 logprob = double(l[t]) - normalizer).
+int oracle_score_row(const float *x, int n, int top, double *logsumexp, int32_t *top1, int32_t *top_ids,
+                     double *top_logprob) {
+  ORACLE_TRY if (!x || n < 1 || top < 0 || top > n || !logsumexp) fail("score arguments");
+  int b = 0;
+  for (int i = 0; i < n; ++i) {
+    if (!std::isfinite(x[i])) fail("non-finite target logits");
+    if (x[i] > x[b]) b = i;
+  }
+  const double mx = x[b];
+  double sum = 0;
+  for (int i = 0; i < n; ++i) sum += std::exp(double(x[i]) - mx);
+  *logsumexp = mx + std::log(sum);
+  if (top1) *top1 = b;
+  std::vector<int> ids(n);
+  for (int i = 0; i < n; ++i) ids[i] = i;
+  std::partial_sort(ids.begin(), ids.begin() + top, ids.end(),
+                    [&](int a, int c) { return x[a] == x[c] ? a < c : x[a] > x[c]; });
+  for (int k = 0; k < top; ++k) {
+    top_ids[k] = ids[k];
+    top_logprob[k] = double(x[ids[k]]) - *logsumexp;
+  }
+  ORACLE_END
+}
+
 // Extended single row: effective (nullable) receives the penalised logits with excluded ids at -inf.
 int oracle_extended_probabilities(const float *x, double *p, int n, double t, double top, int top_k,
                                   const int32_t *history, int history_len, float repetition, float presence,

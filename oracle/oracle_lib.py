@@ -49,6 +49,7 @@ class Oracle:
         L.oracle_sample_v2.argtypes = [P, C.c_int, u64, u64, u32, u32, P]
         L.oracle_verify_v2.argtypes = [P, P, P, C.c_int, C.c_int, C.c_int, u64, u64, P]
         L.oracle_argmax.argtypes = [P, C.c_int, P]
+        L.oracle_score_row.argtypes = [P, C.c_int, C.c_int, P, P, P, P]
         L.oracle_extended_probabilities.argtypes = [P, P, C.c_int, f64, f64, C.c_int, P, C.c_int, f32, f32, f32, P, P]
         L.oracle_sample_rows.argtypes = [P, C.c_int, C.c_int, C.c_int64, f64, f64, C.c_int, P, C.c_int64, P, f32,
                                          f32, f32, P, C.c_int64, P, P, u32, u32, P, P, C.c_int]
@@ -110,6 +111,14 @@ class Oracle:
         out = i32(-1)
         self._check(self.lib.oracle_argmax(_ptr(x), x.size, C.byref(out)))
         return out.value
+
+    def score_row(self, x, top):
+        """(logsumexp, top1, top_ids, top_logprob) of one logits row by the reference's score rule."""
+        x = np.ascontiguousarray(x, np.float32)
+        lse, top1 = C.c_double(), i32(-1)
+        ids, lp = np.empty(top, np.int32), np.empty(top, np.float64)
+        self._check(self.lib.oracle_score_row(_ptr(x), x.size, top, C.byref(lse), C.byref(top1), _ptr(ids), _ptr(lp)))
+        return lse.value, top1.value, ids, lp
 
     def verify(self, drafts, q, p, greedy, seed, step):
         p = np.ascontiguousarray(p, np.float64)

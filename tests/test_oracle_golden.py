@@ -190,3 +190,20 @@ def test_e4m3_roundtrip(oracle):
     assert oracle.lib.oracle_e4m3_encode(1.0625) == 0x38       # halfway 1.0 / 1.125 -> 1.0 (even)
     assert oracle.lib.oracle_e4m3_encode(1.1875) == 0x3A       # halfway 1.125 / 1.25 -> 1.25 (even)
     assert oracle.lib.oracle_e4m3_encode(1e9) == 0x7E and oracle.lib.oracle_e4m3_encode(-1e9) == 0xFE
+
+
+def test_score_row_restatement(oracle):
+    """log_normalizer / top_order (engine/src/server.cpp:178-183, 730-737) restated: against an independent numpy
+    evaluation (math.fsum for the sum, a stable sort for the order), incl. ties."""
+    import math
+    x = oracle.gen_logits(31, 1, 5000)[0]
+    x[100:110] = x.max() + 0.5
+    lse, top1, ids, lp = oracle.score_row(x, 12)
+    m = float(x.max())
+    want = m + math.log(math.fsum(math.exp(float(v) - m) for v in x))
+    assert abs(lse - want) <= 1e-13 * abs(want)
+    order = np.lexsort((np.arange(x.size), -x.astype(np.float64)))[:12]
+    assert top1 == 100 and ids.tolist() == order.tolist()
+    assert np.allclose(lp, x[order].astype(np.float64) - lse, rtol=0, atol=1e-12)
+    with pytest.raises(ValueError):
+        oracle.score_row(np.array([1.0, np.inf], np.float32), 1)
