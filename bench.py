@@ -151,7 +151,7 @@ class HeadSample:
         g = torch.Generator(device=device).manual_seed(99)
         self.ring = [torch.randn(batch, HIDDEN, device=device, generator=g).to(torch.bfloat16) for _ in range(16)]
         self.host_ring = [h.cpu().pin_memory() for h in self.ring]
-        self.hidden = torch.empty_like(self.ring[0])
+        self.hidden = self.ring[0].clone()  # static input buffer of the captured step
         self.a = torch.empty((batch, HIDDEN), dtype=torch.uint8, device=device)
         self.a_scale = torch.empty((batch, HIDDEN // 128), dtype=torch.float32, device=device)
         self.logits = torch.empty((batch, self.vn), dtype=torch.float32, device=device)
