@@ -105,9 +105,12 @@ typedef struct ds41_b200_sample_args {
   int32_t *tokens;            /* [rows] out */
   int32_t *status;            /* [rows] out, see above; may be NULL */
   void *scratch;              /* optional device scratch of ds41_b200_sample_scratch_bytes(rows, vocab) bytes, 16-byte
-                                 aligned.  With it, rows without penalties / bitmask and with top_k <= 64 take the
-                                 streaming path (one pass of independent CTAs + a per-row combine); rows that path
-                                 cannot cover, and calls without scratch, use the cluster kernel.  Same results. */
+                                 aligned.  With it, rows without penalties / bitmask and with top_k <= 64 are tried,
+                                 per row, by two batch-parallel paths before the cluster kernel: from 128 rows on (top_p
+                                 < 1, no top_k, rows 16-byte aligned) the path for wide nuclei (flat distributions:
+                                 five grid-wide kernels), then the streaming path for small nuclei (chunk records + a
+                                 per-row combine).  Rows neither can certify, and calls without scratch, use the
+                                 cluster kernel.  Same results on every path. */
   size_t scratch_bytes;
 } ds41_b200_sample_args;
 size_t ds41_b200_sample_scratch_bytes(int rows, int vocab);
