@@ -514,10 +514,16 @@ __global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
       exact += ((b.m - y) * b.inv_w < edge1) ? 0.0 : w;
     };
     const int vec_end = a.vocab & ~3;  // rows are 16-byte aligned
-#pragma unroll 2
-    for (int id = 4 * tid; id < vec_end; id += 4 * kFT) {
-      const float4 v = __ldg(reinterpret_cast<const float4 *>(x + id));
-      add_tail(v.x); add_tail(v.y); add_tail(v.z); add_tail(v.w);
+    for (int id0 = 4 * tid; id0 < vec_end; id0 += 16 * kFT) {  // four 16-byte loads in flight per thread
+      float4 v[4];
+#pragma unroll
+      for (int u4 = 0; u4 < 4; ++u4) {
+        const int id = id0 + u4 * 4 * kFT;
+        v[u4] = id < vec_end ? __ldg(reinterpret_cast<const float4 *>(x + id))
+                             : make_float4(CUDART_INF_F, CUDART_INF_F, CUDART_INF_F, CUDART_INF_F);  // +inf: not tail
+      }
+#pragma unroll
+      for (int u4 = 0; u4 < 4; ++u4) { add_tail(v[u4].x); add_tail(v[u4].y); add_tail(v[u4].z); add_tail(v[u4].w); }
     }
     for (int id = vec_end + tid; id < a.vocab; id += kFT) add_tail(__ldg(x + id));
     exact = flat_sum(red, exact);
