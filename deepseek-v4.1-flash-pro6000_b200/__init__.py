@@ -90,6 +90,8 @@ def lib():
         L.ds41_b200_verify_scratch_bytes.restype = C.c_size_t
         L.ds41_b200_verify_scratch_bytes.argtypes = [C.c_int, C.c_int]
         L.ds41_b200_score_logits.argtypes = [C.POINTER(ScoreArgs), _P]
+        L.ds41_b200_head_bf16.argtypes = [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P]
+        L.ds41_fuse_head_decode.argtypes = [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P]
         _lib = L
     return _lib
 
@@ -274,6 +276,22 @@ def head_fp8(a, a_scale, w, w_scale, logits=None, error_flag=None):
                                         error_flag.data_ptr() if error_flag is not None else None, _stream()),
                "ds41_b200_head_fp8")
     return logits
+
+
+def head_bf16(x, w_bf16, out=None, decode_symbol=False):
+    """The reference's BF16 head (ds41_fuse_head_decode, components/fuse-head/include/ds41/fuse_head.h:9-10): x fp32
+    [M,K], weights bf16 [N,K] -> fp32 [M,N], bit-identical to the reference plugin.  decode_symbol=True calls the
+    plugin's own entry point, which only accepts N == 129280 and K == 5120."""
+    x = _dev(x, torch.float32, "x")
+    w_bf16 = _dev(w_bf16, torch.bfloat16, "w")
+    M, K = x.shape
+    N = w_bf16.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    fn = lib().ds41_fuse_head_decode if decode_symbol else lib().ds41_b200_head_bf16
+    with torch.cuda.device(x.device):
+        _check(fn(x.data_ptr(), w_bf16.data_ptr(), out.data_ptr(), M, N, K, _stream()), "BF16 head")
+    return out
 
 
 def score_logits(logits, top_n=0):

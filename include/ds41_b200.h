@@ -72,6 +72,18 @@ size_t ds41_fuse_head_fp8_workspace_bytes(int M, int K);
 int ds41_fuse_head_fp8(const void *x_bf16, const void *w_e4m3, const float *w_scale, float *logits, int M, int N,
                        int K, void *workspace, size_t workspace_bytes, int *error_flag, cudaStream_t stream);
 
+/* BF16 head: the reference engine's head plugin symbol, same signature and argument check
+ * (components/fuse-head/include/ds41/fuse_head.h:9-10; src/head_decode.cpp:4-10: 1 <= M <= 6, N == 129280, K == 5120),
+ * x fp32 [M,K], weights bf16 [N,K] row-major, out fp32 [M,N].  The FP32 arithmetic order of the reference kernels
+ * (head_half_tree.cu:7-21: sixteen fused-multiply-add chains over k = l + 16 j, a four-level tree, +0.f) is kept, so
+ * the results equal the reference plugin's bit for bit.  ds41_b200_head_bf16 is the same operator for any N and any K
+ * that is a multiple of 512 with M*K*4 bytes of activations + 66 KB within 227 KB of shared memory (K <= 6656 at
+ * M = 6); weights 16-byte aligned. */
+int ds41_fuse_head_decode(const float *x, const void *weights_bf16, float *out, int M, int N, int K,
+                          cudaStream_t stream);
+int ds41_b200_head_bf16(const float *x, const void *weights_bf16, float *out, int M, int N, int K,
+                        cudaStream_t stream);
+
 /* ---- sampler: logits -> token ids -----------------------------------------------------------------------
  * Replaces, fused and batched on the device, the engine's per-token host sequence
  *   probabilities(logits, T, top_p)  (engine/src/sampling.cpp:205-219 -> spark sampling.cpp:30-38)

@@ -409,6 +409,35 @@ int oracle_argmax(const float *x, int n, int32_t *out) {
   ORACLE_END
 }
 
+// BF16 head in the reference kernels' own arithmetic order (components/fuse-head/src/head_half_tree.cu:7-21 and
+// head_half_tune.cu:7-22): sixteen FP32 chains per output, chain l = fused multiply-adds over k = l, l+16, ... in
+// ascending order; then four tree levels over the chain index (distance 8, 4, 2, 1; a chain without a partner at that
+// distance adds itself, as the width-16 shuffle does, which never reaches chain 0); then + 0.f.
+int oracle_head_bf16(const float *x, const uint16_t *w_bits, float *y, int M, int N, int K) {
+  ORACLE_TRY if (!x || !w_bits || !y || M < 1 || N < 1 || K < 1) fail("bf16 head arguments");
+  for (int n = 0; n < N; ++n)
+    for (int m = 0; m < M; ++m) {
+      float c[16];
+      for (int l = 0; l < 16; ++l) {
+        float acc = 0.f;
+        for (int k = l; k < K; k += 16) {
+          uint32_t bits = uint32_t(w_bits[size_t(n) * K + k]) << 16;
+          float weight;
+          std::memcpy(&weight, &bits, 4);
+          acc = std::fmaf(weight, x[size_t(m) * K + k], acc);
+        }
+        c[l] = acc;
+      }
+      for (int d = 8; d; d >>= 1) {
+        float next[16];
+        for (int i = 0; i < 16; ++i) next[i] = c[i] + (i + d < 16 ? c[i + d] : c[i]);
+        std::memcpy(c, next, sizeof c);
+      }
+      y[size_t(m) * N + n] = c[0] + 0.f;
+    }
+  ORACLE_END
+}
+
 // Score reporting of one row (engine/src/server.cpp:178-183 log_normalizer: max, then the sequential FP64 sum of
 // exp(double(v) - max), result max + log(sum); :730-737 top_order: the first n ids in the order value descending, id
 // ascending; :450-461 logprob = double(l[t]) - normalizer).

@@ -50,6 +50,7 @@ class Oracle:
         L.oracle_verify_v2.argtypes = [P, P, P, C.c_int, C.c_int, C.c_int, u64, u64, P]
         L.oracle_argmax.argtypes = [P, C.c_int, P]
         L.oracle_score_row.argtypes = [P, C.c_int, C.c_int, P, P, P, P]
+        L.oracle_head_bf16.argtypes = [P, P, P, C.c_int, C.c_int, C.c_int]
         L.oracle_extended_probabilities.argtypes = [P, P, C.c_int, f64, f64, C.c_int, P, C.c_int, f32, f32, f32, P, P]
         L.oracle_sample_rows.argtypes = [P, C.c_int, C.c_int, C.c_int64, f64, f64, C.c_int, P, C.c_int64, P, f32,
                                          f32, f32, P, C.c_int64, P, P, u32, u32, P, P, C.c_int]
@@ -111,6 +112,15 @@ class Oracle:
         out = i32(-1)
         self._check(self.lib.oracle_argmax(_ptr(x), x.size, C.byref(out)))
         return out.value
+
+    def head_bf16(self, x, w_bits):
+        """out fp32 [M,N] = x fp32 [M,K] . W^T with W given as bf16 bit patterns uint16 [N,K], in the reference
+        plugin's arithmetic order."""
+        x = np.ascontiguousarray(x, np.float32)
+        w_bits = np.ascontiguousarray(w_bits, np.uint16)
+        y = np.empty((x.shape[0], w_bits.shape[0]), np.float32)
+        self._check(self.lib.oracle_head_bf16(_ptr(x), _ptr(w_bits), _ptr(y), x.shape[0], w_bits.shape[0], x.shape[1]))
+        return y
 
     def score_row(self, x, top):
         """(logsumexp, top1, top_ids, top_logprob) of one logits row by the reference's score rule."""
