@@ -4,8 +4,8 @@
 // ascending order with one fused multiply-add per term, then the chains are added by a four-level tree (distance 8, 4,
 // 2, 1 over the chain index) and +0.f canonicalises a negative zero.  This kernel keeps exactly that order — every
 // intermediate is the same FP32 number — and changes only how the bytes move: a persistent CTA keeps the M activation
-// rows in shared memory, streams 32 weight rows x 512 K at a time through a double buffer with 16-byte cp.async copies
-// (1 KB contiguous per weight row and copy, against 32 bytes per half-warp step in the reference), and each thread runs
+// rows in shared memory, streams 64 weight rows x 256 K at a time through a double buffer with 16-byte cp.async copies
+// (512 bytes contiguous per weight row and copy, against 32 bytes per half-warp step in the reference), and each thread runs
 // the chains of two weight rows so that every activation load feeds two fused multiply-adds.
 // HBM-bound: the BF16 weights, 2*N*K bytes (1.32 GB at N=129280, K=5120), are read exactly once.
 #include "ds41_b200.h"
@@ -17,7 +17,7 @@
 namespace ds41 {
 namespace {
 
-constexpr int kRowsPerCta = 32, kChunkK = 512, kHeadBf16Threads = 16 * kRowsPerCta / 2;  // 256: two rows per thread
+constexpr int kRowsPerCta = 64, kChunkK = 256, kHeadBf16Threads = 16 * kRowsPerCta / 2;  // 512: two rows per thread
 constexpr int kRowPitch = kChunkK * 2 + 32;  // bytes; the 32-byte skew keeps the two rows of a warp on different banks
 
 template <int M>
@@ -26,10 +26,10 @@ __global__ void __launch_bounds__(kHeadBf16Threads) head_bf16_kernel(const float
   extern __shared__ __align__(16) unsigned char smem[];
   float *sx = reinterpret_cast<float *>(smem);                                   // [M][K]
   unsigned char *sw = smem + size_t(M) * K * sizeof(float);                      // [2][kRowsPerCta][kRowPitch]
-  const int tid = threadIdx.x, lane = tid & 15, pair = tid >> 4;                 // rows pair and pair + 16 of the block
+  const int tid = threadIdx.x, lane = tid & 15, pair = tid >> 4;                 // rows pair and pair + 32 of the block
   for (int i = tid; i < M * K; i += kHeadBf16Threads) sx[i] = __ldg(x + i);
   const int blocks = (N + kRowsPerCta - 1) / kRowsPerCta, chunks = K / kChunkK;
-  auto stage = [&](int block, int chunk, int buf) {  // 32 rows x 1 KB, 16 bytes per copy
+  auto stage = [&](int block, int chunk, int buf) {  // 64 rows x 512 bytes, 16 bytes per copy
     unsigned char *dst = sw + size_t(buf) * kRowsPerCta * kRowPitch;
     for (int i = tid; i < kRowsPerCta * (kChunkK * 2 / 16); i += kHeadBf16Threads) {
       const int r = i / (kChunkK * 2 / 16), c = i % (kChunkK * 2 / 16);
@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(kHeadBf16Threads) head_bf16_kernel(const float
       __syncthreads();
       const unsigned char *rows = sw + size_t(buf) * kRowsPerCta * kRowPitch;
       const __nv_bfloat16 *w0 = reinterpret_cast<const __nv_bfloat16 *>(rows + pair * kRowPitch);
-      const __nv_bfloat16 *w1 = reinterpret_cast<const __nv_bfloat16 *>(rows + (pair + 16) * kRowPitch);
+      const __nv_bfloat16 *w1 = reinterpret_cast<const __nv_bfloat16 *>(rows + (pair + kRowsPerCta / 2) * kRowPitch);
       const float *xs = sx + chunk * kChunkK;
 #pragma unroll 4
       for (int k = lane; k < kChunkK; k += 16) {
@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(kHeadBf16Threads) head_bf16_kernel(const float
       __syncthreads();
       buf ^= 1;
     }
-    const int row0 = block * kRowsPerCta + pair, row1 = row0 + 16;
+    const int row0 = block * kRowsPerCta + pair, row1 = row0 + kRowsPerCta / 2;
 #pragma unroll
     for (int m = 0; m < M; ++m) {
       for (int d = 8; d; d >>= 1) {
@@ -118,7 +118,7 @@ extern "C" int ds41_b200_head_bf16(const float *x, const void *weights_bf16, flo
                                    cudaStream_t stream) {
   if (!x || !weights_bf16 || !out || M < 1 || M > 6 || N < 1 || K < kChunkK || K % kChunkK ||
       size_t(M) * K * sizeof(float) + 2 * size_t(kRowsPerCta) * kRowPitch > 227 * 1024)
-    return invalid("BF16 head arguments (1 <= M <= 6, K a multiple of 512, M*K*4 bytes of activations + 66 KB within 227 KB)");
+    return invalid("BF16 head arguments (1 <= M <= 6, K a multiple of 256, M*K*4 bytes of activations + 68 KB within 227 KB)");
   if ((reinterpret_cast<uintptr_t>(weights_bf16) & 15u)) return invalid("BF16 head: weights must be 16-byte aligned");
   cudaError_t e;
   switch (M) {

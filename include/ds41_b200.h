@@ -77,7 +77,7 @@ int ds41_fuse_head_fp8(const void *x_bf16, const void *w_e4m3, const float *w_sc
  * x fp32 [M,K], weights bf16 [N,K] row-major, out fp32 [M,N].  The FP32 arithmetic order of the reference kernels
  * (head_half_tree.cu:7-21: sixteen fused-multiply-add chains over k = l + 16 j, a four-level tree, +0.f) is kept, so
  * the results equal the reference plugin's bit for bit.  ds41_b200_head_bf16 is the same operator for any N and any K
- * that is a multiple of 512 with M*K*4 bytes of activations + 66 KB within 227 KB of shared memory (K <= 6656 at
+ * that is a multiple of 256 with M*K*4 bytes of activations + 68 KB within 227 KB of shared memory (K <= 6656 at
  * M = 6); weights 16-byte aligned. */
 int ds41_fuse_head_decode(const float *x, const void *weights_bf16, float *out, int M, int N, int K,
                           cudaStream_t stream);
