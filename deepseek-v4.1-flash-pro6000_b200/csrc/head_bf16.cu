@@ -24,10 +24,16 @@ template <int M>
 __global__ void __launch_bounds__(kHeadBf16Threads) head_bf16_kernel(const float *x, const __nv_bfloat16 *w, float *y,
                                                                      int N, int K) {
   extern __shared__ __align__(16) unsigned char smem[];
-  float *sx = reinterpret_cast<float *>(smem);                                   // [M][K]
-  unsigned char *sw = smem + size_t(M) * K * sizeof(float);                      // [2][kRowsPerCta][kRowPitch]
+  // activations chain-major: x[m][l + 16 j] at sx[(m * 16 + l) * pitch + j], so that a chain reads four consecutive
+  // terms with one 16-byte load (the pitch of K/16 + 4 floats spreads the sixteen chains over the banks)
+  float *sx = reinterpret_cast<float *>(smem);
+  const int pitch = K / 16 + 4;
+  unsigned char *sw = smem + size_t(M) * 16 * pitch * sizeof(float);             // [2][kRowsPerCta][kRowPitch]
   const int tid = threadIdx.x, lane = tid & 15, pair = tid >> 4;                 // rows pair and pair + 32 of the block
-  for (int i = tid; i < M * K; i += kHeadBf16Threads) sx[i] = __ldg(x + i);
+  for (int i = tid; i < M * K; i += kHeadBf16Threads) {
+    const int m = i / K, k = i - m * K;
+    sx[(m * 16 + (k & 15)) * pitch + (k >> 4)] = __ldg(x + i);
+  }
   const int blocks = (N + kRowsPerCta - 1) / kRowsPerCta, chunks = K / kChunkK;
   auto stage = [&](int block, int chunk, int buf) {  // 64 rows x 512 bytes, 16 bytes per copy
     unsigned char *dst = sw + size_t(buf) * kRowsPerCta * kRowPitch;
@@ -60,15 +66,22 @@ __global__ void __launch_bounds__(kHeadBf16Threads) head_bf16_kernel(const float
       const unsigned char *rows = sw + size_t(buf) * kRowsPerCta * kRowPitch;
       const __nv_bfloat16 *w0 = reinterpret_cast<const __nv_bfloat16 *>(rows + pair * kRowPitch);
       const __nv_bfloat16 *w1 = reinterpret_cast<const __nv_bfloat16 *>(rows + (pair + kRowsPerCta / 2) * kRowPitch);
-      const float *xs = sx + chunk * kChunkK;
-#pragma unroll 4
-      for (int k = lane; k < kChunkK; k += 16) {
-        const float a0 = __bfloat162float(w0[k]), a1 = __bfloat162float(w1[k]);
+      const float *xs = sx + lane * pitch + chunk * (kChunkK / 16);  // this chain's terms of the chunk, row m at + m*16*pitch
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-          const float xv = xs[size_t(m) * K + k];
-          acc0[m] = __fmaf_rn(a0, xv, acc0[m]);
-          acc1[m] = __fmaf_rn(a1, xv, acc1[m]);
+      for (int q = 0; q < kChunkK / 64; ++q) {  // four terms of the chain per round, in ascending k
+        float4 xv[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) xv[m] = *reinterpret_cast<const float4 *>(xs + size_t(m) * 16 * pitch + 4 * q);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int k = lane + 16 * (4 * q + t);
+          const float a0 = __bfloat162float(w0[k]), a1 = __bfloat162float(w1[k]);
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            const float xt = t == 0 ? xv[m].x : t == 1 ? xv[m].y : t == 2 ? xv[m].z : xv[m].w;
+            acc0[m] = __fmaf_rn(a0, xt, acc0[m]);
+            acc1[m] = __fmaf_rn(a1, xt, acc1[m]);
+          }
         }
       }
       __syncthreads();
@@ -90,7 +103,7 @@ __global__ void __launch_bounds__(kHeadBf16Threads) head_bf16_kernel(const float
 
 template <int M>
 cudaError_t launch_head_bf16(const float *x, const void *w, float *y, int N, int K, cudaStream_t stream) {
-  const size_t smem = size_t(M) * K * sizeof(float) + 2 * size_t(kRowsPerCta) * kRowPitch;
+  const size_t smem = size_t(M) * (K + 64) * sizeof(float) + 2 * size_t(kRowsPerCta) * kRowPitch;
   int dev = 0, sms = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -117,7 +130,7 @@ using namespace ds41;
 extern "C" int ds41_b200_head_bf16(const float *x, const void *weights_bf16, float *out, int M, int N, int K,
                                    cudaStream_t stream) {
   if (!x || !weights_bf16 || !out || M < 1 || M > 6 || N < 1 || K < kChunkK || K % kChunkK ||
-      size_t(M) * K * sizeof(float) + 2 * size_t(kRowsPerCta) * kRowPitch > 227 * 1024)
+      size_t(M) * (K + 64) * sizeof(float) + 2 * size_t(kRowsPerCta) * kRowPitch > 227 * 1024)
     return invalid("BF16 head arguments (1 <= M <= 6, K a multiple of 256, M*K*4 bytes of activations + 68 KB within 227 KB)");
   if ((reinterpret_cast<uintptr_t>(weights_bf16) & 15u)) return invalid("BF16 head: weights must be 16-byte aligned");
   cudaError_t e;
