@@ -3,6 +3,7 @@
 and runs too long to be replayed pass after pass).
 
     python deepseek-v4.1-flash-pro6000_b200/profile_cases.py head    [--rows 1024] [--vocab 16384] [--hidden 4096]
+    python deepseek-v4.1-flash-pro6000_b200/profile_cases.py headbf16 [--rows 6]        (the reference's BF16 plugin shape)
     python deepseek-v4.1-flash-pro6000_b200/profile_cases.py sampler [--rows 64] [--dist flat|peaked] [--stream]
     python deepseek-v4.1-flash-pro6000_b200/profile_cases.py verify  [--seqs 8] [--drafts 2]
 
@@ -21,7 +22,7 @@ VOCAB = 129280
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["head", "sampler", "verify"])
+    ap.add_argument("case", choices=["head", "headbf16", "sampler", "verify"])
     ap.add_argument("--rows", type=int, default=None)
     ap.add_argument("--vocab", type=int, default=16384)
     ap.add_argument("--hidden", type=int, default=4096)
@@ -50,6 +51,13 @@ def main():
             pkg.head_fp8(a, a_scale, wq, ws.contiguous(), logits, flag)
         torch.cuda.synchronize()
         assert flag.item() == 0
+    elif args.case == "headbf16":
+        rows = args.rows or 6
+        x = torch.randn(rows, 5120, device=dev, generator=g)
+        w = (0.02 * torch.randn(VOCAB, 5120, device=dev, generator=g)).to(torch.bfloat16)
+        for _ in range(1 + args.repeat):
+            pkg.head_bf16(x, w, decode_symbol=True)
+        torch.cuda.synchronize()
     elif args.case == "sampler":
         rows = args.rows or 64
         if args.dist == "flat":
