@@ -161,10 +161,10 @@ class HeadSample:
         self.status = torch.empty(batch, dtype=torch.int32, device=device)
         self.tokens_host = torch.empty(batch, dtype=torch.int32).pin_memory()
         self.flag = torch.zeros(1, dtype=torch.int32, device=device)
-        # sampler scratch: with it, batches of 128 rows or more go through the batch path for wide nuclei first
-        # (smaller batches of these flat logits go to the cluster kernel directly: the streaming path, which scratch
-        # would also enable, only covers peaked distributions)
-        self.scratch = torch.empty(pkg.sample_scratch_bytes(batch, VOCAB), dtype=torch.uint8, device=device) if batch >= 128 else None
+        # sampler scratch (the batch path: histogram / window / FP64 masses / resolve) and the per-row records the head's
+        # epilogue leaves for it (first maximum, minimum, finiteness), which save the sampler one pass over the logits
+        self.scratch = torch.empty(pkg.sample_scratch_bytes(batch, VOCAB), dtype=torch.uint8, device=device)
+        self.extremes = torch.zeros((batch, 16), dtype=torch.uint8, device=device)
         self.units = batch
         self.h2d, self.d2h = batch * HIDDEN * 2, batch * 4
         # the two kernels that can dominate a step, each timed with its own event pair
@@ -180,16 +180,16 @@ class HeadSample:
         self.graph = None
         self.sharded = None
         self.exchange_note = None
-        # own kernels per step: quantise, head, then the sampler call = flat_stats/hist/window/mass/resolve + the three
-        # predicated fall-through kernels (chunk, combine, row_kernel) for batches >= 128, else row_kernel alone
-        self.launches_per_step = 10 if batch >= 128 else 3
+        # own kernels per step: quantise, head, then the sampler call = flat_hist / flat_window / flat_mass / flat_resolve
+        # and the cluster kernel's persistent grid for rows handed on (returns at once when there are none)
+        self.launches_per_step = 7
         if world > 1:
             self.sharded = import_module("ds41_b200.sharded").ShardedDecodeTail(pkg, device, batch, self.v0, self.vn,
                                                                               VOCAB, temperature, top_p, strategy)
             strategy = self.sharded.strategy  # "candidates" if the peer buffers could not be mapped
             self.exchange_note = self.sharded.exchange_error
-            local_rows = -(-batch // world)
-            self.launches_per_step = (10 if local_rows >= 128 else 3) if strategy == "rows" else 6
+            # rows: quantise, head (+ peer stores), flat_stats / hist / window / mass / resolve, cluster kernel
+            self.launches_per_step = 8 if strategy == "rows" else 6
 
     def step(self, i, hidden=None, ev=None):
         pkg = self.pkg
@@ -217,12 +217,12 @@ class HeadSample:
             return
         if ev:
             ev[0].record()
-        pkg.head_fp8(self.a, self.a_scale, self.wq, self.ws, self.logits, self.flag)
+        pkg.head_fp8(self.a, self.a_scale, self.wq, self.ws, self.logits, self.flag, row_extremes=self.extremes)
         if ev:
             ev[1].record()
             ev[2].record()
         pkg.sample_logits(self.logits, self.t, self.top_p, self.seeds, self.steps, tokens=self.tokens,
-                          status=self.status, scratch=self.scratch)
+                          status=self.status, scratch=self.scratch, row_extremes=self.extremes)
         if ev:
             ev[3].record()
 

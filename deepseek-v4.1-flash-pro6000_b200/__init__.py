@@ -44,7 +44,8 @@ class SampleArgs(C.Structure):
                 ("temperature", _f64), ("top_p", _f64), ("top_k", _i32), ("repetition", _f32), ("presence", _f32),
                 ("frequency", _f32), ("history", _P), ("history_stride", _i64), ("history_len", _P), ("mask", _P),
                 ("mask_stride", _i64), ("seeds", _P), ("steps", _P), ("slot", _u32), ("purpose", _u32),
-                ("tokens", _P), ("status", _P), ("scratch", _P), ("scratch_bytes", C.c_size_t)]
+                ("tokens", _P), ("status", _P), ("scratch", _P), ("scratch_bytes", C.c_size_t),
+                ("row_extremes", _P)]
 
 
 class VerifyArgs(C.Structure):
@@ -84,6 +85,7 @@ def lib():
         L.ds41_b200_verify_logits_static_max_rows.restype = C.c_int
         L.ds41_b200_quantize_activations.argtypes = [_P, _P, _P, C.c_int, C.c_int, _P]
         L.ds41_b200_head_fp8.argtypes = [_P, _P, _P, _P, _P, _i64, C.c_int, C.c_int, C.c_int, _P, _P]
+        L.ds41_b200_head_fp8_stats.argtypes = [_P, _P, _P, _P, _P, _i64, C.c_int, C.c_int, C.c_int, _P, _P, _P]
         L.ds41_fuse_head_fp8_workspace_bytes.restype = C.c_size_t
         L.ds41_fuse_head_fp8_workspace_bytes.argtypes = [C.c_int, C.c_int]
         L.ds41_fuse_head_fp8.argtypes = [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, _P, C.c_size_t, _P, _P]
@@ -157,11 +159,12 @@ def sample_scratch_bytes(rows, vocab):
 
 def sample_logits(logits, temperature, top_p, seeds, steps, slot=0, purpose=Purpose.Target, top_k=0, history=None,
                   history_len=None, repetition=1.0, presence=0.0, frequency=0.0, mask=None, tokens=None, status=None,
-                  scratch="auto"):
+                  scratch="auto", row_extremes=None):
     """Batched probabilities() + sample() / argmax() on device logits [rows, vocab] (fp32).
 
     seeds/steps: int64 CUDA tensors holding the uint64 Philox key and attempt counter of each row.
-    scratch: "auto" (allocate what the streaming path needs), None (cluster kernel only) or a uint8 CUDA tensor.
+    scratch: "auto" (allocate what the batch-parallel paths need), None (cluster kernel only) or a uint8 CUDA tensor.
+    row_extremes: the uint8 [rows, 16] records head_fp8(..., row_extremes=...) wrote for these logits, or None.
     Returns (tokens int32 [rows], status int32 [rows]); see ds41_b200.h for the status words."""
     logits = _dev(logits, torch.float32, "logits") if logits.is_contiguous() else logits
     if logits.dim() != 2 or logits.stride(1) != 1 or not logits.is_cuda or logits.dtype != torch.float32:
@@ -195,6 +198,7 @@ def sample_logits(logits, temperature, top_p, seeds, steps, slot=0, purpose=Purp
         scratch = torch.empty(sample_scratch_bytes(rows, vocab), dtype=torch.uint8, device=logits.device) if usable else None
     a.scratch = scratch.data_ptr() if scratch is not None else None
     a.scratch_bytes = scratch.numel() if scratch is not None else 0
+    a.row_extremes = row_extremes.data_ptr() if row_extremes is not None else None
     with torch.cuda.device(logits.device):
         _check(lib().ds41_b200_sample_logits(C.byref(a), _stream()), "ds41_b200_sample_logits")
     return tokens, status
@@ -262,19 +266,30 @@ def quantize_activations(x_bf16, a=None, a_scale=None):
     return a, a_scale
 
 
-def head_fp8(a, a_scale, w, w_scale, logits=None, error_flag=None):
-    """Block-scaled FP8 head GEMM: a uint8 [M,K] (e4m3), w uint8 [N,K] (e4m3) -> fp32 logits [M,N]."""
+def head_fp8(a, a_scale, w, w_scale, logits=None, error_flag=None, row_extremes=None):
+    """Block-scaled FP8 head GEMM: a uint8 [M,K] (e4m3), w uint8 [N,K] (e4m3) -> fp32 logits [M,N].
+    row_extremes: optional uint8 CUDA tensor [M, 16]; the head then also leaves each row's first maximum, minimum and
+    finiteness there (ds41_b200_head_fp8_stats) for sample_logits(row_extremes=...)."""
     a = _dev(a, torch.uint8, "a"); w = _dev(w, torch.uint8, "w")
     a_scale = _dev(a_scale, torch.float32, "a_scale"); w_scale = _dev(w_scale, torch.float32, "w_scale")
     M, K = a.shape
     N = w.shape[0]
     if logits is None:
         logits = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    flag = error_flag.data_ptr() if error_flag is not None else None
     with torch.cuda.device(a.device):
-        _check(lib().ds41_b200_head_fp8(a.data_ptr(), a_scale.data_ptr(), w.data_ptr(), w_scale.data_ptr(),
-                                        logits.data_ptr(), logits.stride(0), M, N, K,
-                                        error_flag.data_ptr() if error_flag is not None else None, _stream()),
-               "ds41_b200_head_fp8")
+        if row_extremes is None:
+            _check(lib().ds41_b200_head_fp8(a.data_ptr(), a_scale.data_ptr(), w.data_ptr(), w_scale.data_ptr(),
+                                            logits.data_ptr(), logits.stride(0), M, N, K, flag, _stream()),
+                   "ds41_b200_head_fp8")
+        else:
+            row_extremes = _dev(row_extremes, torch.uint8, "row_extremes")
+            if row_extremes.numel() < 16 * M:
+                raise ValueError("row_extremes must hold 16 bytes per row")
+            _check(lib().ds41_b200_head_fp8_stats(a.data_ptr(), a_scale.data_ptr(), w.data_ptr(), w_scale.data_ptr(),
+                                                  logits.data_ptr(), logits.stride(0), M, N, K,
+                                                  row_extremes.data_ptr(), flag, _stream()),
+                   "ds41_b200_head_fp8_stats")
     return logits
 
 

@@ -18,11 +18,13 @@
 // (tcgen05.ld), hand the accumulator back at once, scale and add in fp32 registers.
 // Every wait is bounded; on expiry the kernel raises *error_flag, frees its TMEM and returns.
 #include "ds41_b200.h"
+#include "flat.cuh"
 #include "host_error.h"
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
+#include <math_constants.h>
 #include <stdint.h>
 #include <stdlib.h>
 
@@ -162,6 +164,10 @@ struct HeadArgs {
   // writes them with plain stores, so the vocabulary-to-row transposition rides on the GEMM.  rows_per_owner == 0: off.
   float *owner_base[kMaxOwners];
   int rows_per_owner, col_offset;
+  // Optional per-row statistics for the sampler (zero-initialised by the host): every epilogue thread keeps the first
+  // maximum, the minimum and a finiteness flag of the logits it produces for its batch row and merges them with atomic
+  // maxima when it leaves the row, so the sampler's own pass over the logits for these three numbers can be skipped.
+  HeadRowStats *row_stats;
   int stages;            // shared-memory stages of the TMA ring (host: HeadSmem::stages)
   int group;             // K blocks per stage: every row of a weight tile is fetched as group*128 contiguous bytes
 };
@@ -265,10 +271,29 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     int table_bt = -1;
     bool alive = true;  // warp-uniform; once false the remaining tiles are walked without waiting or computing,
                         // so that all epilogue threads still meet at every named barrier
+    // running statistics of this thread's batch row over the tiles of one batch tile (vocabulary tiles come in
+    // ascending order, so a strict comparison keeps the first maximum)
+    float st_best = -CUDART_INF_F, st_low = CUDART_INF_F, st_bad = 0.f;
+    int st_id = 0x7fffffff;
+    auto flush_stats = [&](int bt_of) {
+      const int m = bt_of * kRows + row;
+      if (p.row_stats && st_id != 0x7fffffff && row < kRows && m < p.M) {
+        auto ordered = [](float v) {
+          const uint32_t bits = __float_as_uint(v == 0.f ? 0.f : v);  // -0 and +0 are the same logit
+          return bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u);
+        };
+        HeadRowStats *rs = p.row_stats + m;
+        atomicMax(&rs->max_key, (unsigned long long)(ordered(st_best)) << 32 | (0xffffffffu - uint32_t(st_id)));
+        atomicMax(&rs->min_key, ~ordered(st_low));
+        if (st_bad != st_bad) atomicOr(&rs->flags, 1u);
+      }
+      st_best = -CUDART_INF_F; st_low = CUDART_INF_F; st_bad = 0.f; st_id = 0x7fffffff;
+    };
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       const int nt = tile / b_tiles, bt = tile % b_tiles;
       if (bt != table_bt) {  // activation scales of this batch tile: sa[kb][row] (a grid that is a multiple of b_tiles
                              // keeps bt fixed per CTA, so this normally happens once)
+        if (table_bt >= 0) flush_stats(table_bt);
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiActive) : "memory");  // readers of the previous table are done
         for (int i = et; i < kblocks * kRows; i += kEpiActive) {
           const int r = i / kblocks, kb = i % kblocks, m = bt * kRows + r;
@@ -322,6 +347,28 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       // 32 rows with 16 bytes each; an 8 x 8 transpose of the 16-byte column groups across the lanes that share
       // l % 4 (butterflies at lane distances 4, 8, 16) turns that into 4 rows with 128 contiguous bytes each, which is
       // what a peer GPU's memory wants to be written with (and the local L2 as well).
+      if (alive && p.row_stats) {
+        const int n0 = nt * kTileN + group * kMyCols;
+        if (n0 + kMyCols <= p.N) {
+#pragma unroll
+          for (int c = 0; c < kMyCols; ++c) {
+            const float v = sum[c];
+            st_bad = fmaf(v, 0.f, st_bad);  // NaN once any logit is NaN or infinite
+            if (v > st_best) { st_best = v; st_id = n0 + c; }
+            st_low = fminf(st_low, v);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < kMyCols; ++c) {
+            const float v = sum[c];
+            if (n0 + c < p.N) {
+              st_bad = fmaf(v, 0.f, st_bad);
+              if (v > st_best) { st_best = v; st_id = n0 + c; }
+              st_low = fminf(st_low, v);
+            }
+          }
+        }
+      }
       if (alive) {
 #pragma unroll
        for (int half = 0; half < kMyCols / 32; ++half) {
@@ -371,6 +418,7 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
        }
       }
     }
+    if (alive && table_bt >= 0) flush_stats(table_bt);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -490,6 +538,22 @@ extern "C" int ds41_b200_head_fp8(const void *a_e4m3, const float *a_scale, cons
   HeadArgs p{};
   p.a_scale = a_scale; p.w_scale = w_scale; p.logits = logits; p.ldl = logits_stride;
   p.M = M; p.N = N; p.K = K; p.error_flag = error_flag;
+  return run_head(a_e4m3, a_scale, w_e4m3, w_scale, p, stream);
+}
+
+extern "C" int ds41_b200_head_fp8_stats(const void *a_e4m3, const float *a_scale, const void *w_e4m3, const float *w_scale,
+                                        float *logits, int64_t logits_stride, int M, int N, int K, void *row_extremes,
+                                        int *error_flag, cudaStream_t stream) {
+  if (!a_e4m3 || !a_scale || !w_e4m3 || !w_scale || !logits || M < 1 || N < 1 || K < 128 || K % 128 || K > 16384 ||
+      logits_stride < N || !row_extremes || (reinterpret_cast<uintptr_t>(row_extremes) & 15u))
+    return invalid("head arguments");
+  static_assert(sizeof(HeadRowStats) == DS41_B200_ROW_EXTREMES_BYTES, "row record size");
+  cudaError_t e = cudaMemsetAsync(row_extremes, 0, size_t(M) * sizeof(HeadRowStats), stream);
+  if (e != cudaSuccess) return int(e);
+  HeadArgs p{};
+  p.a_scale = a_scale; p.w_scale = w_scale; p.logits = logits; p.ldl = logits_stride;
+  p.M = M; p.N = N; p.K = K; p.error_flag = error_flag;
+  p.row_stats = static_cast<HeadRowStats *>(row_extremes);
   return run_head(a_e4m3, a_scale, w_e4m3, w_scale, p, stream);
 }
 

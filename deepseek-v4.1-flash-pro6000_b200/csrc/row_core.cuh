@@ -383,6 +383,9 @@ __device__ CutResult find_cut(RowCtx &c, float max_logit, float first_width, int
   unsigned long long target_fix = 0;
   double target_mass = 0;
   int chosen = -1;  // bin to resolve; -2 = every active id survives
+  bool plateau = false;  // the bin to resolve holds more than kListCap ids, all with the logit plateau_y
+  float plateau_y = 0.f;
+  int plateau_n = 0;
   for (int level = 0;; ++level) {
     for (int j = c.tid; j < kBins; j += kThreads) { s->bin_count[j] = 0; s->bin_mass[j] = 0; }
     __syncthreads();
@@ -488,7 +491,33 @@ __device__ CutResult find_cut(RowCtx &c, float max_logit, float first_width, int
       count_before_level = before_c; mass_before_level = before_m;
       continue;
     }
-    if (in_bin > kListCap) {  // refine the crossing bin
+    if (in_bin > kListCap) {  // refine the crossing bin -- unless all of its ids share one logit (a plateau of ties)
+      float lo_y = CUDART_INF_F, hi_y = -CUDART_INF_F;
+      for (int it = 0; it < c.region; it += 32) {
+        const int j = c.warp * c.region + it + c.lane;
+        if (j >= c.len) continue;
+        const float y = s->y[j];
+        if (!active(y, c.begin + j) || classify(L, max_logit - y) != found) continue;
+        lo_y = fminf(lo_y, y); hi_y = fmaxf(hi_y, y);
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) {
+        lo_y = fminf(lo_y, __shfl_xor_sync(0xffffffffu, lo_y, o));
+        hi_y = fmaxf(hi_y, __shfl_xor_sync(0xffffffffu, hi_y, o));
+      }
+      if (c.lane == 0) { s->red_f[c.warp] = lo_y; s->red_d[c.warp] = double(hi_y); }
+      __syncthreads();
+      for (int w = 0; w < kWarps; ++w) { lo_y = fminf(lo_y, s->red_f[w]); hi_y = fmaxf(hi_y, float(s->red_d[w])); }
+      __syncthreads();
+      Slot span{};
+      span.f[0] = lo_y; span.f[1] = hi_y;
+      const Slot *spans = exchange(c, span);
+      for (int r = 0; r < c.nranks; ++r) { lo_y = fminf(lo_y, spans[r].f[0]); hi_y = fmaxf(hi_y, spans[r].f[1]); }
+      if (lo_y == hi_y) {  // equal logits have equal weights: the cut inside the plateau follows from arithmetic
+        plateau = true; plateau_y = lo_y; plateau_n = in_bin;
+        chosen = found;
+        break;
+      }
       if (L.n == kMaxLevels) { out.error = -4; return out; }
       L.pick[L.n - 1] = found;
       L.lo[L.n] = L.lo[L.n - 1] + float(found) / L.inv_w[L.n - 1];
@@ -523,8 +552,10 @@ __device__ CutResult find_cut(RowCtx &c, float max_logit, float first_width, int
         ++before_count;
         if (kMass) before_mass += weight(y);
       } else if (b == chosen) {
-        const int slot = atomicAdd(list_count0, 1);
-        if (slot < kListCap) { list_y0[slot] = y; list_id0[slot] = id; }
+        if (!plateau) {
+          const int slot = atomicAdd(list_count0, 1);
+          if (slot < kListCap) { list_y0[slot] = y; list_id0[slot] = id; }
+        }
       } else {
         ++after_count;
       }
@@ -538,6 +569,99 @@ __device__ CutResult find_cut(RowCtx &c, float max_logit, float first_width, int
     int n_before = 0, n_after = 0;
     for (int r = 0; r < c.nranks; ++r) { mass_before += all[r].d[0]; n_before += all[r].i[0]; n_after += all[r].i[1]; }
 
+    if (plateau) {
+      // ---- the cut inside a plateau of plateau_n equal logits (reference: stable order, ties keep the lower id, one
+      // weight added per kept id: sampling.cpp:34-36).  Every thread of the cluster computes the same numbers.
+      long long k = 0;  // ids of the plateau that are kept
+      int direction = 0, amb = 0;
+      double mass = mass_before;
+      if constexpr (!kMass) {
+        k = (long long)target_count - n_before;
+        if (k < 1) direction = -1; else if (k > plateau_n) direction = 1;
+      } else {
+        const double w = weight(plateau_y);
+        const double lo = target_mass * (1.0 - rel_bound), hi = target_mass * (1.0 + rel_bound);
+        if (n_before > 0 && mass_before >= target_mass) direction = -1;
+        else {
+          const double need = (target_mass - mass_before) / w;
+          k = need > double(plateau_n) + 2.0 ? (long long)plateau_n + 1 : (long long)need;
+          if (k < 1) k = 1;
+          while (k <= plateau_n && mass_before + double(k) * w < target_mass) ++k;
+          while (k > 1 && mass_before + double(k - 1) * w >= target_mass) --k;
+          if (k > plateau_n) {
+            if (n_after > 0) direction = 1;
+            else { k = plateau_n; mass = mass_before + double(k) * w; amb = !(mass < lo); }  // every id kept
+          } else {
+            mass = mass_before + double(k) * w;
+            const double prev = mass_before + double(k - 1) * w;
+            amb = (mass < hi) || (prev >= lo);
+          }
+        }
+      }
+      if (direction != 0) { out.error = -4; return out; }  // the histogram mis-picked a crowded bin's neighbour: not handled
+      // the k-th id of the plateau in ascending id order: counts per warp region, per CTA, then a walk of one region
+      int mine = 0;
+      for (int it = 0; it < c.region; it += 32) {
+        const int j = c.warp * c.region + it + c.lane;
+        if (j < c.len && s->y[j] == plateau_y && active(s->y[j], c.begin + j)) ++mine;
+      }
+      mine = __reduce_add_sync(0xffffffffu, mine);
+      if (c.lane == 0) s->red_i[c.warp] = mine;
+      __syncthreads();
+      int cta_total = 0;
+      for (int w2 = 0; w2 < kWarps; ++w2) cta_total += s->red_i[w2];
+      Slot cnt{};
+      cnt.i[0] = cta_total;
+      const Slot *cnts = exchange(c, cnt);
+      long long skip = k - 1;  // tied ids before the wanted one
+      int owner = -1;
+      for (int r = 0; r < c.nranks; ++r) {
+        if (owner < 0 && skip < cnts[r].i[0]) owner = r;
+        if (owner < 0) skip -= cnts[r].i[0];
+      }
+      Slot pick{};
+      pick.i[0] = -1;
+      if (owner == c.rank) {
+        int ow = -1;
+        long long left = skip;
+        for (int w2 = 0; w2 < kWarps; ++w2) {
+          if (ow < 0 && left < s->red_i[w2]) ow = w2;
+          if (ow < 0) left -= s->red_i[w2];
+        }
+        if (c.warp == ow) {
+          int found_id = -1;
+          int remaining = int(left);
+          for (int it = 0; it < c.region && found_id < 0; it += 32) {
+            const int j = ow * c.region + it + c.lane;
+            const bool tied = j < c.len && s->y[j] == plateau_y && active(s->y[j], c.begin + j);
+            const unsigned ballot = __ballot_sync(0xffffffffu, tied);
+            const int here = __popc(ballot);
+            if (remaining < here) {
+              unsigned m = ballot;
+              for (int q = 0; q < remaining; ++q) m &= m - 1;  // drop the lowest `remaining` set bits
+              found_id = c.begin + ow * c.region + it + (__ffs(m) - 1);
+            } else {
+              remaining -= here;
+            }
+          }
+          if (c.lane == 0) s->bcast_i[0] = found_id;
+        }
+        __syncthreads();
+        pick.i[0] = s->bcast_i[0];
+        __syncthreads();
+      }
+      const Slot *picks = exchange(c, pick);
+      int cut_id = -1;
+      for (int r = 0; r < c.nranks; ++r) cut_id = max(cut_id, picks[r].i[0]);
+      if (cut_id < 0) { out.error = -4; return out; }
+      const bool all_kept = k == plateau_n && n_after == 0;
+      out.cut.y = all_kept ? -CUDART_INF_F : plateau_y;
+      out.cut.id = all_kept ? -1 : cut_id;
+      out.kept = n_before + int(k);
+      out.e_kept = mass;
+      out.ambiguous = amb;
+      return out;
+    }
     Slot verdict{};
     double *sorted_e = reinterpret_cast<double *>(s->bin_mass);  // local bins are dead once the totals exist
     if (c.rank == 0) {

@@ -28,6 +28,7 @@ struct RowArgs {
   int32_t *status;
   RowStats *stats;
   int only_uncovered;  // 1: process only rows the streaming path reported as not covered, leave the others alone
+  const int *pending;  // optional, with only_uncovered: number of such rows; 0 = nothing to do, every CTA returns at once
   int rows;            // set by launch_rows: a cluster walks rows cluster, cluster + clusters, ... below this
 };
 
@@ -181,7 +182,7 @@ __device__ __forceinline__ void row_body(const RowArgs &a, RowCtx &c, RowSmem *s
   // ---- history counts (16-bit counters packed in pairs; remote shared-memory atomics route each id to its owner)
   const bool penalised = a.history != nullptr && (a.repetition != 1.f || a.presence != 0.f || a.frequency != 0.f);
   int hist_len = penalised ? (a.history_len ? a.history_len[row] : int(a.history_stride)) : 0;
-  const bool bad_history = hist_len < 0 || hist_len > 65535;
+  const bool bad_history = hist_len < 0 || hist_len > 65535 || (long long)hist_len > a.history_stride;
   if (bad_history) hist_len = 0;
   if (hist_len > 0) {
     for (int j = c.tid; j < kSliceCap / 2; j += kThreads) s->u.count_pairs[j] = 0;
@@ -392,6 +393,7 @@ template <int kMode>
 __global__ void __launch_bounds__(kThreads, 2) row_kernel(RowArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   RowSmem *s = reinterpret_cast<RowSmem *>(smem_raw);
+  if (a.only_uncovered && a.pending && *a.pending == 0) return;  // the same in every CTA of the grid
   RowCtx c = make_ctx(s, a.vocab);
   const int clusters = int(gridDim.x) / c.nranks;
   for (int row = int(blockIdx.x) / c.nranks; row < a.rows; row += clusters) {

@@ -110,34 +110,45 @@ extern "C" int ds41_b200_sample_logits(const ds41_b200_sample_args *p, cudaStrea
   a.tokens = p->tokens; a.status = p->status; a.stats = nullptr;
   const bool penalised = p->history && (p->repetition != 1.f || p->presence != 0.f || p->frequency != 0.f);
   const size_t need = ds41_b200_sample_scratch_bytes(p->rows, p->vocab);
-  const bool streaming = p->scratch && p->scratch_bytes >= need && !(reinterpret_cast<uintptr_t>(p->scratch) & 15u) &&
-                         !penalised && !p->mask && p->top_k <= kCand &&
-                         (p->top_p < 1.0 || p->top_k > 0 || p->temperature == 0);  // a full-vocabulary draw is never covered
-  if (!streaming) return int(launch_rows<kModeSample>(a, p->rows, stream));
+  const bool scratch_ok = p->scratch && p->scratch_bytes >= need && !(reinterpret_cast<uintptr_t>(p->scratch) & 15u) &&
+                          !penalised && !p->mask && p->top_k <= kCand;
+  // Batches of rows that are only cut by top-p first go through the batch path; it answers the rows it fits and marks
+  // the others -8 / -9, and the paths below then only touch those.
+  const bool flat = scratch_ok && flat_shape(p->rows, p->vocab) && p->top_k == 0 && p->temperature > 0 &&
+                    p->logits_stride != 0 && p->logits_stride % 4 == 0 && !(reinterpret_cast<uintptr_t>(p->logits) & 15u);
+  // the streaming path covers small nuclei only: a full-vocabulary draw never fits its candidate sets
+  const bool streaming = scratch_ok && (p->top_p < 1.0 || p->top_k > 0 || p->temperature == 0);
+  if (!flat && !streaming) return int(launch_rows<kModeSample>(a, p->rows, stream));
   const int chunks = chunks_for(p->vocab);
   ChunkRecord *records = static_cast<ChunkRecord *>(p->scratch);
   int32_t *status = p->status ? p->status : reinterpret_cast<int32_t *>(records + size_t(p->rows) * chunks);
   cudaError_t e;
-  // Large batches of top-p rows first go through the batch path for wide nuclei; it answers the rows it fits and
-  // marks the others -8, and the paths below then only touch those.
-  const bool flat = flat_shape(p->rows, p->vocab) && p->top_k == 0 && p->top_p < 1.0 && p->temperature > 0 &&
-                    p->logits_stride != 0 && p->logits_stride % 4 == 0 && !(reinterpret_cast<uintptr_t>(p->logits) & 15u);
   if (flat) {
     FlatArgs f{};
     f.logits = p->logits; f.stride = p->logits_stride; f.vocab = p->vocab; f.rows = p->rows;
     f.t = a.temperature; f.top_p = p->top_p; f.seeds = p->seeds; f.steps = p->steps; f.slot = p->slot;
     f.purpose = p->purpose; f.tokens = p->tokens; f.status = status;
-    e = launch_flat(f, static_cast<unsigned char *>(p->scratch) + streaming_bytes(p->rows, p->vocab), stream);
+    f.head_stats = static_cast<const HeadRowStats *>(p->row_extremes);
+    void *flat_scratch = static_cast<unsigned char *>(p->scratch) + streaming_bytes(p->rows, p->vocab);
+    e = launch_flat(f, flat_scratch, stream);
+    if (e != cudaSuccess) return int(e);
+    // what the batch path could not take (plateaus of equal logits at the cut, ranges beyond its exponent limit) goes to
+    // the cluster kernel: a small persistent grid that returns at once when no row was handed on
+    a.status = status;
+    a.only_uncovered = 1;
+    a.pending = flat_pending(flat_scratch);
+    return int(launch_rows<kModeSample>(a, p->rows, stream));
+  }
+  if (streaming) {
+    // streaming path: chunk records -> combine -> cluster kernel only for the rows the combine could not cover
+    ChunkArgs c{p->logits, p->logits_stride, p->vocab, 0, chunks, a.temperature, records, nullptr};
+    e = launch_chunks(c, p->rows, stream);
+    if (e != cudaSuccess) return int(e);
+    CombineArgs m{records, p->rows, 1, chunks, p->vocab, a.temperature, p->top_p, p->top_k, p->seeds, p->steps, p->slot,
+                  p->purpose, p->tokens, status, nullptr, 0};
+    e = launch_combine(m, false, stream);
     if (e != cudaSuccess) return int(e);
   }
-  // streaming path: chunk records -> combine -> cluster kernel only for the rows the combine could not cover
-  ChunkArgs c{p->logits, p->logits_stride, p->vocab, 0, chunks, a.temperature, records, flat ? status : nullptr};
-  e = launch_chunks(c, p->rows, stream);
-  if (e != cudaSuccess) return int(e);
-  CombineArgs m{records, p->rows, 1, chunks, p->vocab, a.temperature, p->top_p, p->top_k, p->seeds, p->steps, p->slot,
-                p->purpose, p->tokens, status, nullptr, flat ? 1 : 0};
-  e = launch_combine(m, false, stream);
-  if (e != cudaSuccess) return int(e);
   a.status = status;
   a.only_uncovered = 1;
   return int(launch_rows<kModeSample>(a, p->rows, stream));
@@ -151,12 +162,12 @@ __global__ void exp_probe_kernel(const double *x, double *out, int n) {
 }  // namespace ds41
 
 namespace ds41 {
-cudaError_t launch_hist_probe(const float *y, float max_logit, float min_logit, double t, double *out, int n, cudaStream_t stream);
+cudaError_t launch_flat_weight_probe(const float *y, float max_logit, double t, double *out, int n, cudaStream_t stream);
 }
-extern "C" int ds41_b200_test_hist_weight(const float *y, float max_logit, float min_logit, double temperature,
-                                          double *out, int n, cudaStream_t stream) {
-  if (!y || !out || n < 1 || !(temperature > 0) || !(min_logit < max_logit)) return invalid("histogram probe arguments");
-  return int(ds41::launch_hist_probe(y, max_logit, min_logit, temperature, out, n, stream));
+extern "C" int ds41_b200_test_batch_weight(const float *y, float max_logit, double temperature, double *out, int n,
+                                           cudaStream_t stream) {
+  if (!y || !out || n < 1 || !(temperature > 0)) return invalid("weight probe arguments");
+  return int(ds41::launch_flat_weight_probe(y, max_logit, temperature, out, n, stream));
 }
 
 extern "C" int ds41_b200_test_exp_nonpos(const double *x, double *out, int n, cudaStream_t stream) {

@@ -221,10 +221,9 @@ class RowExchange:
         self.full.zero_()
         self.word = torch.zeros(1, dtype=torch.int32, device=device)
         self.packed = torch.full((2, self.rows_per_owner), -1, dtype=torch.int32, device=device)
-        # scratch enables the batch path for wide nuclei (128 rows or more); with fewer rows the cluster kernel is the
-        # right tool for the flat logits this exchange exists for, and it needs none
+        # scratch enables the sampler's batch path (grid-wide kernels over this rank's rows)
         self.scratch = (torch.empty(pkg.sample_scratch_bytes(self.my_rows, vocab), dtype=torch.uint8, device=device)
-                        if self.my_rows >= 128 else None)
+                        if self.my_rows else None)
         self.everyone = torch.empty((self.world, 2, self.rows_per_owner), dtype=torch.int32, device=device)
         if self.world > 1:
             dist.barrier(group=group)  # every buffer exists and is mapped before anyone writes

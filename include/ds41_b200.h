@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define DS41_B200_ABI 1
+#define DS41_B200_ABI 2
 #define DS41_B200_MAX_VOCAB 131072 /* 8 cluster CTAs x 16384 staged logits */
 #define DS41_B200_MAX_HISTORY 65535 /* 16-bit shared-memory counters */
 
@@ -33,11 +33,11 @@ extern "C" {
 #define DS41_B200_ROW_NONFINITE (-1)      /* a logit is NaN/Inf   (sampling.cpp:32 "nonfinite logits") */
 #define DS41_B200_ROW_EMPTY (-2)          /* bitmask allows no id (sampling.cpp:19 "empty residual support") */
 #define DS41_B200_ROW_PENALTY_OVERFLOW (-3)
-#define DS41_B200_ROW_TIES (-4)           /* more than 1024 equal logits straddle a top-k / top-p cut */
+#define DS41_B200_ROW_TIES (-4)           /* the cut search gave up: more than 1024 ids, not all equal, inside one bin of its finest level */
 #define DS41_B200_ROW_TIMEOUT (-5)        /* a bounded device-side wait expired */
 #define DS41_B200_ROW_DRAFT (-6)          /* draft id out of range or impossible under q (sampling.cpp:44,47) */
 #define DS41_B200_ROW_NOT_COVERED (-8)    /* sharded combine: the candidates of some rank may not contain the whole nucleus; redo the row from full logits */
-#define DS41_B200_ROW_HISTORY (-7)        /* history_len[r] negative or above DS41_B200_MAX_HISTORY */
+#define DS41_B200_ROW_HISTORY (-7)        /* history_len[r] negative, above DS41_B200_MAX_HISTORY or above history_stride */
 
 /* Same layout as ds41_spark_result (spark.h:106-108). */
 typedef struct ds41_spark_result {
@@ -66,6 +66,14 @@ int ds41_b200_quantize_activations(const void *x_bf16, void *a_e4m3, float *a_sc
 int ds41_b200_head_fp8(const void *a_e4m3, const float *a_scale, const void *w_e4m3, const float *w_scale,
                        float *logits, int64_t logits_stride, int M, int N, int K, int *error_flag,
                        cudaStream_t stream);
+/* The same head, which also leaves per-row records (first maximum and its id, minimum, finiteness) of the logits it
+ * produced in row_extremes [M] (DS41_B200_ROW_EXTREMES_BYTES each, 16-byte aligned, cleared by the call): pass them to
+ * ds41_b200_sample_logits as args->row_extremes and the sampler's batch path skips its own first pass over the logits.
+ * No counterpart in the reference (its sampler runs on the host). */
+#define DS41_B200_ROW_EXTREMES_BYTES 16
+int ds41_b200_head_fp8_stats(const void *a_e4m3, const float *a_scale, const void *w_e4m3, const float *w_scale,
+                             float *logits, int64_t logits_stride, int M, int N, int K, void *row_extremes,
+                             int *error_flag, cudaStream_t stream);
 /* Quantise + multiply in one call: x_bf16 [M,K] -> logits fp32 [M,N] (stride N).  workspace: caller-owned device
  * memory of ds41_fuse_head_fp8_workspace_bytes(M,K) bytes, 256-byte aligned. */
 size_t ds41_fuse_head_fp8_workspace_bytes(int M, int K);
@@ -118,12 +126,14 @@ typedef struct ds41_b200_sample_args {
   int32_t *status;            /* [rows] out, see above; may be NULL */
   void *scratch;              /* optional device scratch of ds41_b200_sample_scratch_bytes(rows, vocab) bytes, 16-byte
                                  aligned.  With it, rows without penalties / bitmask and with top_k <= 64 are tried,
-                                 per row, by two batch-parallel paths before the cluster kernel: from 128 rows on (top_p
-                                 < 1, no top_k, rows 16-byte aligned) the path for wide nuclei (flat distributions:
-                                 five grid-wide kernels), then the streaming path for small nuclei (chunk records + a
-                                 per-row combine).  Rows neither can certify, and calls without scratch, use the
-                                 cluster kernel.  Same results on every path. */
+                                 per row, by two batch-parallel paths before the cluster kernel: without top_k (rows
+                                 16-byte aligned, vocab >= 16384) the batch path (grid-wide kernels: histogram,
+                                 window, FP64 masses, resolve), then the streaming path for small nuclei (chunk
+                                 records + a per-row combine).  Rows neither can certify, and calls without scratch,
+                                 use the cluster kernel.  Same results on every path. */
   size_t scratch_bytes;
+  const void *row_extremes;   /* optional: the [rows] records ds41_b200_head_fp8_stats wrote for these logits (16 bytes
+                                 each); the batch path then skips its own maximum / minimum pass.  NULL otherwise. */
 } ds41_b200_sample_args;
 size_t ds41_b200_sample_scratch_bytes(int rows, int vocab);
 int ds41_b200_sample_logits(const ds41_b200_sample_args *args, cudaStream_t stream);
@@ -253,11 +263,11 @@ int ds41_b200_score_logits(const ds41_b200_score_args *args, cudaStream_t stream
  * out[i] = the samplers' own exp(x[i]) for x <= 0 (device pointers), so that its error can be measured against a
  * reference exponential.  No counterpart in the reference. */
 int ds41_b200_test_exp_nonpos(const double *x, double *out, int n, cudaStream_t stream);
-/* out[i] = the weight exp((y[i] - max_logit) / temperature) as the batch sampler's histogram pass measures it (fixed
- * point relative to the near edge of the id's bin, bins over [min_logit, max_logit]; device pointers), for the test of
- * its stated error bound. */
-int ds41_b200_test_hist_weight(const float *y, float max_logit, float min_logit, double temperature, double *out,
-                               int n, cudaStream_t stream);
+/* out[i] = the weight exp((y[i] - max_logit) / temperature) as the sampler's batch path computes it in its FP64 pass
+ * (y[i] <= max_logit, (max_logit - y[i]) * log2(e) / temperature <= 600; device pointers), for the test of its error
+ * bound against a reference exponential. */
+int ds41_b200_test_batch_weight(const float *y, float max_logit, double temperature, double *out, int n,
+                                cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -126,6 +126,39 @@ def test_row_errors_are_reported_in_band(pkg, oracle):
     assert (wst[[1, 2, 4]] == -1).all()
     ok = [0, 3, 5]
     assert (tok[ok] == want[ok]).all() and (st[ok] >= 0).all()
+    # a history length beyond the row's stride would read the next row's history: rejected in band
+    hist = np.zeros((6, 32), np.int32)
+    x2 = oracle.gen_logits(9, 6, 4097)
+    tok, st = run(pkg, x2, 1.0, 0.9, np.zeros(6), np.arange(6), history=hist, repetition=1.2,
+                  history_len=[32, 33, 0, -1, 70000, 5])
+    assert st[[1, 3, 4]].tolist() == [-7, -7, -7] and (tok[[1, 3, 4]] == -1).all()
+    assert (st[[0, 2, 5]] >= 0).all()
+
+
+@pytest.mark.parametrize("scratch", [None, "auto"])
+@pytest.mark.parametrize("top_k,top", [(0, 0.9013), (0, 0.5017), (0, 1.0), (3000, 1.0), (3000, 0.7123), (20000, 0.95113)])
+def test_tie_plateaus_at_the_cut(pkg, oracle, top_k, top, scratch):
+    """Thousands of equal logits straddling the top-p / top-k cut: the reference keeps them in id order
+    (stable sort, engine/third_party/spark/src/sampling.cpp:34-37), so the number kept follows from arithmetic and the
+    last kept id from counting.  Rows: all equal; a 5,000-id plateau that holds nearly all the mass; a plateau on top of
+    a spread row; two plateaus; logits quantised to halves."""
+    vocab = 129280
+    x = oracle.gen_logits(55, 6, vocab)
+    x[0] = 1.0
+    x[1] = -3.0; x[1, 1000:6000] = 2.0
+    x[2, 50000:55000] = x[2].max() + 1.0
+    x[3, ::2] = 1.5; x[3, 1::2] = -1.0
+    x[4] = np.round(x[4] * 2) / 2
+    x[5, 7] = 30.0; x[5, 10000:16000] = 29.0
+    seeds, steps = np.arange(6) + 41, np.arange(6) * 3 + 7
+    for rep in range(3):
+        want, wst = oracle.sample_rows(x, 0.6, top, seeds, steps + rep, top_k=top_k, threads=6)
+        tok, st = run(pkg, x, 0.6, top, seeds, steps + rep, top_k=top_k, scratch=scratch)
+        assert (st >= 0).all(), st
+        # (top-p values whose product with a plateau's size is not an integer: at an exact product the reference's own
+        # rounding decides whether one more id is kept, and the row is then reported as uncertified, not guessed)
+        assert (st == 0).all(), st
+        assert (tok == want).all(), (top_k, top, tok, want, st)
 
 
 def test_argument_errors(pkg):
