@@ -593,7 +593,7 @@ __global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
       e[i] = r < n ? exp_nonpos((double(ys[i]) - m64) * inv_t) : 0.0;
     }
     const double through0 = mass_before + flat_prefix2(red, e[0], e[1]), through1 = through0 + e[1];
-    const double rel = 2.0 * (double(a.vocab) + kFlatWeightUlps) * kU;
+    const double rel = 2.0 * (double(a.vocab) + kFlatWeightUlps) * kU * a.bound_scale;
     const double target_p = a.top_p * z, lo = target_p * (1.0 - rel), hi = target_p * (1.0 + rel);
     if (tid == 0) { found_at = 0x7fffffff; cut_amb = 0; }
     __syncthreads();
@@ -637,7 +637,7 @@ __global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
   __syncthreads();
   const double total = cut_mass[1];
   const double u = philox_uniform(a.seeds[row], a.steps[row], a.slot, a.purpose);
-  const double target = u * total, slack = 2.0 * (double(kept) + kFlatWeightUlps) * kU * total;
+  const double target = u * total, slack = 2.0 * (double(kept) + kFlatWeightUlps) * kU * total * a.bound_scale;
   if (tid < kFlatSubs / 2) {
     int mine = -1;
     if (k0 > 0 && target < pre0) mine = 2 * tid;

@@ -39,7 +39,7 @@ struct FlatInfo {
   int pad[2];
 };
 struct FlatScratch {
-  int *pending;                // [4]: rows handed on to the cluster kernel (status -8 / -9)   (zeroed every call)
+  int *pending;                // [4]: rows handed on to the cluster kernel (status -8 / -9); rows replayed   (zeroed every call)
   int *lcount;                 // [rows][4]: window list length, histogram field overflow flag   (zeroed every call)
   unsigned long long *hist;    // [rows][kFlatBins]: count << 32 | sum of the ids' positions inside the bin
   FlatPartial *partial;        // [rows][kFlatMaxParts]
@@ -57,6 +57,7 @@ struct FlatArgs {
   uint32_t slot, purpose;
   int32_t *tokens, *status;    // status is required here
   const HeadRowStats *head_stats;  // optional [rows]: maximum / minimum / finiteness already known (skips the first pass)
+  double bound_scale;              // 1; larger values widen the certification bounds (a test hook: more rows get flagged)
   FlatScratch s;
 };
 

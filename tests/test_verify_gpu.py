@@ -55,7 +55,7 @@ def same(got, want):
         assert list(g["tokens"][:g["emitted"]]) == list(w["tokens"][:w["emitted"]])
 
 
-@pytest.mark.parametrize("t,top,sigma", [(0.6, 0.95, 0.35), (1.0, 1.0, 0.5), (1.0, 0.9, 1.0), (0.0, 1.0, 0.5)])
+@pytest.mark.parametrize("t,top,sigma", [(0.6, 0.95, 0.30), (1.0, 1.0, 0.5), (1.0, 0.9, 1.0), (0.0, 1.0, 0.5)])
 @pytest.mark.parametrize("drafts", [0, 2, 5])
 def test_config3_verification(pkg, oracle, t, top, sigma, drafts):
     """BASELINE config 3 shape: sequences x (1 target + drafts) rows, V=129280."""
