@@ -37,6 +37,7 @@ extern "C" {
 #define DS41_B200_ROW_TIMEOUT (-5)        /* a bounded device-side wait expired */
 #define DS41_B200_ROW_DRAFT (-6)          /* draft id out of range or impossible under q (sampling.cpp:44,47) */
 #define DS41_B200_ROW_NOT_COVERED (-8)    /* sharded combine: the candidates of some rank may not contain the whole nucleus; redo the row from full logits */
+#define DS41_B200_ROW_NOT_NORMALIZED (-10) /* a probability row does not sum to 1 within 1e-8 (sampling.cpp:15) */
 #define DS41_B200_ROW_HISTORY (-7)        /* history_len[r] negative, above DS41_B200_MAX_HISTORY or above history_stride */
 
 /* Same layout as ds41_spark_result (spark.h:106-108). */
@@ -173,6 +174,47 @@ int ds41_b200_verify_logits(const ds41_b200_verify_args *args, cudaStream_t stre
  * allocates.  All calls share the array, so calls that could overlap on the GPU must be serialised by the caller. */
 int ds41_b200_verify_logits_static_max_rows(void);
 int ds41_b200_verify_logits_static(const ds41_b200_verify_args *args, cudaStream_t stream);
+
+/* ---- operators on probability rows: the reference sampler's C ABI on the device ------------------------------------------
+ * For callers that keep the reference's own interface (logits -> probability row -> sample / verify:
+ * engine/include/ds41/engine.hpp:211-227) instead of the fused calls above.  Every sum runs on one thread in index
+ * order, as the reference's host loops do, so for the same probability rows the tokens and accept / reject records are
+ * the reference's bit for bit; ds41_b200_probabilities follows ds41_spark_probabilities operation by operation and can
+ * differ from the host's rows only in the last place of exp().  One CTA per row or transaction, milliseconds per
+ * full-vocabulary row: compatibility and reporting paths, not the decode-rate path.
+ *   ds41_b200_probabilities         <- ds41_spark_probabilities (spark.h:115; sampling.cpp:30-38), temperature floor of
+ *                                      the engine adapter (engine/src/sampling.cpp:209-210); non-finite rows: status -1
+ *   ds41_b200_sample_probabilities  <- ds41_spark_sample_v2     (spark.h:131; sampling.cpp:12-21,59), row r at the
+ *                                      address (seeds[r], steps[r], slot, purpose); rows that are not a probability
+ *                                      measure get token -1 and status -1 / -10 / -2
+ *   ds41_b200_verify_probabilities  <- ds41_spark_verify_v2     (spark.h:132; sampling.cpp:39-56), `sequences`
+ *                                      transactions; q [sequences, drafts, vocab], p [sequences, drafts+1, vocab]
+ *   ds41_spark_sample_gpu_v2 / ds41_spark_verify_gpu_v2: the reference's device sampler ABI itself (spark.h:133-134;
+ *   third_party/spark/src/sampling.cu:24-39,71-72): FP32 measures normalised in FP64, one row / one transaction, result
+ *   in caller-owned device memory, data errors in band (token -1 / emitted -1). */
+typedef struct ds41_b200_prob_args {
+  uint32_t struct_bytes;
+  int32_t rows, vocab;
+  const float *logits;       /* [rows, logits_stride] */
+  int64_t logits_stride;
+  double temperature, top_p;
+  double *probabilities;     /* [rows, vocab] out */
+  int32_t *status;           /* [rows] out */
+  void *scratch;             /* ds41_b200_probabilities_scratch_bytes(rows) bytes, 16-byte aligned */
+  size_t scratch_bytes;
+} ds41_b200_prob_args;
+size_t ds41_b200_probabilities_scratch_bytes(int rows);
+int ds41_b200_probabilities(const ds41_b200_prob_args *args, cudaStream_t stream);
+int ds41_b200_sample_probabilities(const double *p, int rows, int vocab, int64_t stride, const uint64_t *seeds,
+                                   const uint64_t *steps, uint32_t slot, uint32_t purpose, int32_t *tokens,
+                                   int32_t *status, cudaStream_t stream);
+int ds41_b200_verify_probabilities(const int32_t *draft_ids, const double *q, const double *p, int sequences,
+                                   int drafts, int vocab, int greedy, const uint64_t *seeds, const uint64_t *steps,
+                                   ds41_spark_result *results, int32_t *status, cudaStream_t stream);
+int ds41_spark_sample_gpu_v2(const float *p, int vocab, uint64_t seed, uint64_t step, uint32_t slot, uint32_t purpose,
+                             int32_t *token, void *stream);
+int ds41_spark_verify_gpu_v2(const int32_t *draft_ids, const float *q, const float *p, int drafts, int vocab,
+                             int greedy, uint64_t seed, uint64_t step, ds41_spark_result *result, void *stream);
 
 /* ---- vocabulary-sharded sampling (several GPUs, one rank per GPU) -----------------------------------------------
  * No counterpart in the reference (single GPU, no collectives: scripts/run.py:228).  Rank r owns the logits of the
