@@ -94,6 +94,9 @@ def lib():
         L.ds41_b200_score_logits.argtypes = [C.POINTER(ScoreArgs), _P]
         L.ds41_b200_head_bf16.argtypes = [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P]
         L.ds41_fuse_head_decode.argtypes = [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P]
+        L.ds41_dense_head_compact.argtypes = [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P]
+        L.ds41_b200_markov_logits.argtypes = [_P, _P, _P, _P, C.c_int, _P]
+        L.ds41_b200_final_norm.argtypes = [_P, _P, _P, _P, C.c_int, C.c_int, _f32, _P]
         _lib = L
     return _lib
 
@@ -306,6 +309,54 @@ def head_bf16(x, w_bf16, out=None, decode_symbol=False):
     fn = lib().ds41_fuse_head_decode if decode_symbol else lib().ds41_b200_head_bf16
     with torch.cuda.device(x.device):
         _check(fn(x.data_ptr(), w_bf16.data_ptr(), out.data_ptr(), M, N, K, _stream()), "BF16 head")
+    return out
+
+
+def head_compact(x, w_bf16, out=None):
+    """The drafter's BF16 head (ds41_dense_head_compact, components/dense/src/compact.cu:10-24,44-50): x fp32 [M,K]
+    (M <= 8), weights bf16 [N,K] -> fp32 [M,N], bit-identical to the reference kernel."""
+    x = _dev(x, torch.float32, "x")
+    w_bf16 = _dev(w_bf16, torch.bfloat16, "w")
+    M, K = x.shape
+    N = w_bf16.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(lib().ds41_dense_head_compact(x.data_ptr(), w_bf16.data_ptr(), out.data_ptr(), M, N, K, _stream()),
+               "ds41_dense_head_compact")
+    return out
+
+
+def markov_logits(draft_row, markov_weight, embedding, out=None):
+    """Draft logits of one position: draft_row fp32 [V] + markov_weight bf16 [V,256] . embedding bf16 [256]
+    (engine/third_party/spark/src/forward.cu:46,135-139)."""
+    draft_row = _dev(draft_row, torch.float32, "draft_row")
+    markov_weight = _dev(markov_weight, torch.bfloat16, "markov_weight")
+    embedding = _dev(embedding, torch.bfloat16, "embedding")
+    if markov_weight.shape != (draft_row.numel(), 256) or embedding.numel() != 256:
+        raise ValueError("markov_weight must be [V,256] and embedding [256]")
+    if out is None:
+        out = torch.empty_like(draft_row)
+    with torch.cuda.device(draft_row.device):
+        _check(lib().ds41_b200_markov_logits(draft_row.data_ptr(), markov_weight.data_ptr(), embedding.data_ptr(),
+                                             out.data_ptr(), draft_row.numel(), _stream()), "ds41_b200_markov_logits")
+    return out
+
+
+def final_norm(h, pre, norm_weight, eps=1e-20, out=None):
+    """The head's prologue (engine/src/hotpath/batch.inc:487-492): h bf16 [M,4,K], pre fp32 [M,4], norm_weight bf16 [K]
+    -> fp32 [M,K] (HC-pre mix, RMSNorm, rounded to bf16, promoted)."""
+    h = _dev(h, torch.bfloat16, "h")
+    pre = _dev(pre, torch.float32, "pre")
+    norm_weight = _dev(norm_weight, torch.bfloat16, "norm_weight")
+    M, four, K = h.shape
+    if four != 4 or pre.shape != (M, 4) or norm_weight.numel() != K:
+        raise ValueError("h must be [M,4,K], pre [M,4], norm_weight [K]")
+    if out is None:
+        out = torch.empty((M, K), dtype=torch.float32, device=h.device)
+    with torch.cuda.device(h.device):
+        _check(lib().ds41_b200_final_norm(h.data_ptr(), pre.data_ptr(), norm_weight.data_ptr(), out.data_ptr(), M, K,
+                                          eps, _stream()), "ds41_b200_final_norm")
     return out
 
 

@@ -93,6 +93,27 @@ int ds41_fuse_head_decode(const float *x, const void *weights_bf16, float *out, 
 int ds41_b200_head_bf16(const float *x, const void *weights_bf16, float *out, int M, int N, int K,
                         cudaStream_t stream);
 
+/* Drafter head: the reference's own symbol and argument check (components/dense/include/ds41/dense.h;
+ * src/compact.cu:10-24,44-50: 1 <= M <= 8, K a multiple of 256), x fp32 [M,K], weights bf16 [N,K], y fp32 [M,N].  The
+ * reference kernel's FP32 order is kept (four fused-multiply-add chains per lane over 8-wide loads,
+ * (a0+a1)+(a2+a3), 32-lane shuffle-down tree), so the results equal the reference's bit for bit.  Additional limits of
+ * this implementation: M*K*4 bytes within 224 KB of shared memory, x and weights 16-byte aligned. */
+int ds41_dense_head_compact(const float *x, const void *w_bf16, float *y, int M, int N, int K, cudaStream_t stream);
+/* Draft logits of one position: logits[n] = draft_row[n] + bias[n], bias = markov_weight [vocab,256] (bf16) times the
+ * previous token's Markov embedding [256] (bf16, promoted to fp32): the reference's markov() + add_bias
+ * (engine/third_party/spark/src/forward.cu:46,135-139) in one kernel.  The reference forms the bias with a library GEMV
+ * whose summation order is not specified; here it is the compact head's order for K = 256, followed by the reference's
+ * single rounded addition. */
+int ds41_b200_markov_logits(const float *draft_row, const void *markov_weight_bf16, const void *embedding_bf16,
+                            float *logits, int vocab, cudaStream_t stream);
+/* What the reference runs in front of the target head (engine/src/hotpath/batch.inc:487-492): HC-pre mix of the four
+ * streams h [M,4,K] (bf16) with pre [M,4] -> RMSNorm with norm_weight [K] (bf16), eps -> bf16 -> fp32 x [M,K], as one
+ * kernel with the arithmetic and the M-dependent reduction geometry of ds41_dense_hc_pre, ds41_dense_rms and
+ * ds41_dense_promote (components/dense/src/ops.cu:10-27,45-48,102,110-112): bit-identical to running those three.
+ * 1 <= M <= 8, K a multiple of 4 in 128..16384. */
+int ds41_b200_final_norm(const void *h_bf16, const float *pre, const void *norm_weight_bf16, float *x_f32, int M, int K,
+                         float eps, cudaStream_t stream);
+
 /* ---- sampler: logits -> token ids -----------------------------------------------------------------------
  * Replaces, fused and batched on the device, the engine's per-token host sequence
  *   probabilities(logits, T, top_p)  (engine/src/sampling.cpp:205-219 -> spark sampling.cpp:30-38)

@@ -438,6 +438,118 @@ int oracle_head_bf16(const float *x, const uint16_t *w_bits, float *y, int M, in
   ORACLE_END
 }
 
+static float bf16_value(uint16_t bits) {
+  uint32_t wide = uint32_t(bits) << 16;
+  float v;
+  std::memcpy(&v, &wide, 4);
+  return v;
+}
+static uint16_t bf16_round(float v) {  // round to nearest even, as __float2bfloat16_rn (finite inputs)
+  uint32_t bits;
+  std::memcpy(&bits, &v, 4);
+  if ((bits & 0x7fffffffu) > 0x7f800000u) return uint16_t((bits >> 16) | 0x40);
+  bits += 0x7fffu + ((bits >> 16) & 1u);
+  return uint16_t(bits >> 16);
+}
+
+// The drafter's BF16 head in the reference kernel's own arithmetic order (components/dense/src/compact.cu:10-24):
+// 32 lanes per output; lane l takes k = 8 l + 256 i; element j of its eight goes to accumulator j % 4 by fused
+// multiply-add; (a0 + a1) + (a2 + a3); then five shuffle-down levels (distance 16, 8, 4, 2, 1: lane i adds lane i + d,
+// lanes without a partner add their own value, which never reaches lane 0).
+int oracle_head_compact(const float *x, const uint16_t *w_bits, float *y, int M, int N, int K) {
+  ORACLE_TRY if (!x || !w_bits || !y || M < 1 || M > 8 || N < 1 || K < 256 || K % 256) fail("compact head arguments");
+  for (int n = 0; n < N; ++n)
+    for (int m = 0; m < M; ++m) {
+      float lane_sum[32];
+      for (int l = 0; l < 32; ++l) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int k = l * 8; k < K; k += 256)
+          for (int j = 0; j < 8; ++j)
+            acc[j & 3] = std::fmaf(bf16_value(w_bits[size_t(n) * K + k + j]), x[size_t(m) * K + k + j], acc[j & 3]);
+        lane_sum[l] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+      }
+      for (int d = 16; d; d >>= 1) {
+        float next[32];
+        for (int i = 0; i < 32; ++i) next[i] = lane_sum[i] + (i + d < 32 ? lane_sum[i + d] : lane_sum[i]);
+        std::memcpy(lane_sum, next, sizeof lane_sum);
+      }
+      y[size_t(m) * N + n] = lane_sum[0];
+    }
+  ORACLE_END
+}
+
+// Draft logits of one position: U + W_markov . emb (engine/third_party/spark/src/forward.cu:46,135-139), the dot product
+// in the compact head's order for K = 256, then one rounded addition.
+int oracle_markov_logits(const float *u, const uint16_t *w_bits, const uint16_t *emb_bits, float *out, int vocab) {
+  ORACLE_TRY if (!u || !w_bits || !emb_bits || !out || vocab < 1) fail("Markov logits arguments");
+  float e[256];
+  for (int k = 0; k < 256; ++k) e[k] = bf16_value(emb_bits[k]);
+  std::vector<float> bias(vocab);
+  int rc = oracle_head_compact(e, w_bits, bias.data(), 1, vocab, 256);
+  if (rc) return rc;
+  for (int n = 0; n < vocab; ++n) out[n] = u[n] + bias[n];
+  ORACLE_END
+}
+
+// HC-pre mix -> RMSNorm -> BF16 -> FP32 (engine/src/hotpath/batch.inc:487-492; components/dense/src/ops.cu:10-27,45-48,
+// 102,110-112) with the reference's reduction geometry.  The device takes rsqrtf() of mean + eps; this restatement takes
+// 1 / sqrt in FP32, which can differ from it in the last place, so a comparison with the device allows the BF16 result
+// to move by one unit in a few entries (the bit-exact comparison is against the reference kernels themselves).
+int oracle_final_norm(const uint16_t *h_bits, const float *pre, const uint16_t *w_bits, float *out, int M, int K, float eps) {
+  ORACLE_TRY if (!h_bits || !pre || !w_bits || !out || M < 1 || M > 8 || K < 128 || K % 4) fail("final norm arguments");
+  int height = 1;
+  while (height * 2 <= M && height * 2 <= 16) height *= 2;
+  int n = 1;
+  while (n * 2 <= K / 4 && n * 2 <= 512) n *= 2;
+  const int width = n < 512 / height ? n : 512 / height;
+  const int threads = K / width >= height * 16 ? width * height : width;
+  std::vector<uint16_t> x(K);
+  std::vector<float> sh(threads), sum(threads);
+  for (int row = 0; row < M; ++row) {
+    for (int k = 0; k < K; ++k) {
+      float s = 0.f;
+      for (int j = 0; j < 4; ++j) s = s + pre[row * 4 + j] * bf16_value(h_bits[(size_t(row) * 4 + j) * K + k]);
+      x[k] = bf16_round(s);
+    }
+    for (int t = 0; t < threads; ++t) {
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int i = t * 4; i < K; i += threads * 4)
+        for (int j = 0; j < 4; ++j)
+          if (i + j < K) {
+            const float z = bf16_value(x[i + j]);
+            v[j] = v[j] + z * z;
+          }
+      sum[t] = ((v[0] + v[1]) + v[2]) + v[3];
+      sh[t] = sum[t];
+    }
+    for (int d = width / 2; d >= 32; d >>= 1) {          // halving inside each segment of `width` threads
+      std::vector<float> next = sh;
+      for (int t = 0; t < threads; ++t)
+        if (t % width < d) { sum[t] = sum[t] + sh[t + d]; next[t] = sum[t]; }
+      sh = next;
+    }
+    for (int d = 16; d; d >>= 1) {                        // shuffle-down inside every warp
+      std::vector<float> next = sum;
+      for (int t = 0; t < threads; ++t) {
+        const int lane = t & 31;
+        next[t] = sum[t] + (lane + d < 32 && t + d < threads ? sum[t + d] : sum[t]);
+      }
+      sum = next;
+    }
+    for (int t = 0; t < threads; ++t)
+      if (t % width == 0) sh[t] = sum[t];
+    for (int d = (threads / width) / 2; d; d >>= 1) {     // halving over the segments
+      std::vector<float> next = sh;
+      for (int t = 0; t < threads; ++t)
+        if (t % width == 0 && t / width < d) { sum[t] = sum[t] + sh[t + d * width]; next[t] = sum[t]; }
+      sh = next;
+    }
+    const float rstd = 1.f / std::sqrt(sh[0] * (1.f / K) + eps);
+    for (int k = 0; k < K; ++k) out[size_t(row) * K + k] = bf16_value(bf16_round((bf16_value(x[k]) * rstd) * bf16_value(w_bits[k])));
+  }
+  ORACLE_END
+}
+
 // Score reporting of one row (engine/src/server.cpp:178-183 log_normalizer: max, then the sequential FP64 sum of
 // exp(double(v) - max), result max + log(sum); :730-737 top_order: the first n ids in the order value descending, id
 // ascending; :450-461 logprob = double(l[t]) - normalizer).

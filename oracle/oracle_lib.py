@@ -51,6 +51,9 @@ class Oracle:
         L.oracle_argmax.argtypes = [P, C.c_int, P]
         L.oracle_score_row.argtypes = [P, C.c_int, C.c_int, P, P, P, P]
         L.oracle_head_bf16.argtypes = [P, P, P, C.c_int, C.c_int, C.c_int]
+        L.oracle_head_compact.argtypes = [P, P, P, C.c_int, C.c_int, C.c_int]
+        L.oracle_markov_logits.argtypes = [P, P, P, P, C.c_int]
+        L.oracle_final_norm.argtypes = [P, P, P, P, C.c_int, C.c_int, f32]
         L.oracle_extended_probabilities.argtypes = [P, P, C.c_int, f64, f64, C.c_int, P, C.c_int, f32, f32, f32, P, P]
         L.oracle_sample_rows.argtypes = [P, C.c_int, C.c_int, C.c_int64, f64, f64, C.c_int, P, C.c_int64, P, f32,
                                          f32, f32, P, C.c_int64, P, P, u32, u32, P, P, C.c_int]
@@ -121,6 +124,31 @@ class Oracle:
         y = np.empty((x.shape[0], w_bits.shape[0]), np.float32)
         self._check(self.lib.oracle_head_bf16(_ptr(x), _ptr(w_bits), _ptr(y), x.shape[0], w_bits.shape[0], x.shape[1]))
         return y
+
+    def head_compact(self, x, w_bits):
+        """The drafter's BF16 head (components/dense/src/compact.cu) in the reference kernel's arithmetic order."""
+        x = np.ascontiguousarray(x, np.float32)
+        w_bits = np.ascontiguousarray(w_bits, np.uint16)
+        y = np.empty((x.shape[0], w_bits.shape[0]), np.float32)
+        self._check(self.lib.oracle_head_compact(_ptr(x), _ptr(w_bits), _ptr(y), x.shape[0], w_bits.shape[0], x.shape[1]))
+        return y
+
+    def markov_logits(self, u, w_bits, emb_bits):
+        u = np.ascontiguousarray(u, np.float32)
+        w_bits = np.ascontiguousarray(w_bits, np.uint16)
+        emb_bits = np.ascontiguousarray(emb_bits, np.uint16)
+        out = np.empty(u.size, np.float32)
+        self._check(self.lib.oracle_markov_logits(_ptr(u), _ptr(w_bits), _ptr(emb_bits), _ptr(out), u.size))
+        return out
+
+    def final_norm(self, h_bits, pre, w_bits, eps=1e-20):
+        h_bits = np.ascontiguousarray(h_bits, np.uint16)     # [M, 4, K]
+        pre = np.ascontiguousarray(pre, np.float32)           # [M, 4]
+        w_bits = np.ascontiguousarray(w_bits, np.uint16)
+        M, _, K = h_bits.shape
+        out = np.empty((M, K), np.float32)
+        self._check(self.lib.oracle_final_norm(_ptr(h_bits), _ptr(pre), _ptr(w_bits), _ptr(out), M, K, eps))
+        return out
 
     def score_row(self, x, top):
         """(logsumexp, top1, top_ids, top_logprob) of one logits row by the reference's score rule."""
@@ -327,3 +355,22 @@ class Reference:
     def attempt_counter_take2(self, first):
         threw = C.c_int()
         return self.lib.ref_attempt_counter_take2(first, C.byref(threw)), bool(threw.value)
+
+
+class ReferenceGpu:
+    """The reference's own CUDA kernels (fuse-head; dense compact head, hc_pre, rms, promote), compiled in place for
+    sm_100a by oracle/Makefile into oracle/_ref.  Calls take raw device pointers (ints) and a stream."""
+
+    def __init__(self):
+        fh = os.path.join(HERE, "_ref", "libds41_ref_fusehead.so")
+        de = os.path.join(HERE, "_ref", "libds41_ref_dense.so")
+        self.available = os.path.exists(fh) and os.path.exists(de)
+        if not self.available:
+            return
+        self.fusehead, self.dense = C.CDLL(fh), C.CDLL(de)
+        self.fusehead.ds41_fuse_head_decode.argtypes = [P, P, P, C.c_int, C.c_int, C.c_int, P]
+        self.fusehead.ds41_fuse_head_half_tree.argtypes = [P, P, P, C.c_int, C.c_int, C.c_int, P]
+        self.dense.ds41_dense_head_compact.argtypes = [P, P, P, C.c_int, C.c_int, C.c_int, P]
+        self.dense.ds41_dense_hc_pre.argtypes = [P, P, P, C.c_int, C.c_int, P]
+        self.dense.ds41_dense_rms.argtypes = [P, P, P, C.c_int, C.c_int, f32, P]
+        self.dense.ds41_dense_promote.argtypes = [P, P, C.c_int, P]
