@@ -94,6 +94,7 @@ def lib():
         L.ds41_b200_score_logits.argtypes = [C.POINTER(ScoreArgs), _P]
         L.ds41_b200_head_bf16.argtypes = [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P]
         L.ds41_fuse_head_decode.argtypes = [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P]
+        L.ds41_b200_logits_sha256.argtypes = [_P, C.c_int, C.c_int, _i64, _P, _P]
         L.ds41_dense_head_compact.argtypes = [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P]
         L.ds41_b200_markov_logits.argtypes = [_P, _P, _P, _P, C.c_int, _P]
         L.ds41_b200_final_norm.argtypes = [_P, _P, _P, _P, C.c_int, C.c_int, _f32, _P]
@@ -378,6 +379,19 @@ def score_logits(logits, top_n=0):
     with torch.cuda.device(dev):
         _check(lib().ds41_b200_score_logits(C.byref(a), _stream()), "ds41_b200_score_logits")
     return lse, top1, ids, lp, status
+
+
+def logits_sha256(logits):
+    """SHA-256 of every row's fp32 logits (the logits_sha256 of the reference's score event, server.cpp:184-197), as
+    hexadecimal strings."""
+    if logits.dim() != 2 or logits.stride(1) != 1 or not logits.is_cuda or logits.dtype != torch.float32:
+        raise ValueError("logits must be a CUDA fp32 [rows, vocab] tensor with unit inner stride")
+    rows, vocab = logits.shape
+    out = torch.empty((rows, 32), dtype=torch.uint8, device=logits.device)
+    with torch.cuda.device(logits.device):
+        _check(lib().ds41_b200_logits_sha256(logits.data_ptr(), rows, vocab, logits.stride(0), out.data_ptr(), _stream()),
+               "ds41_b200_logits_sha256")
+    return [bytes(r).hex() for r in out.cpu().numpy()]
 
 
 def fuse_head_fp8_workspace_bytes(M, K):

@@ -25,6 +25,121 @@ SHARD_ROW_BYTES = 544
 NOT_COVERED = -8
 
 
+class CollectiveFailure(RuntimeError):
+    """A collective of the sharded step did not complete (a peer never arrived, left, or the communicator reported an
+    error).  Raised on every surviving rank; the process group is unusable afterwards."""
+
+
+class StepGuard:
+    """Host-side failure detection around the collectives of the sharded decode tail.
+
+    The reference has no collectives; what this guards is the exchange this library adds.  Three mechanisms, none of
+    which touches a GPU's state:
+      * every collective is issued with a work handle.  On host tensors (gloo) the handle is waited on with
+        `timeout_s`; on device tensors the wait is stream-ordered (no host block) and the handle is kept until
+        `finish()`, which polls a CUDA event with the same time limit instead of blocking in a synchronize that a
+        dead peer would never release, and then reads the handles' recorded exceptions (the process group's
+        asynchronous error state);
+      * a rank that stops between steps says so in the rendezvous store (`leave()`); `before_step()` reads that
+        counter every `check_every` steps, so the others stop before their next launch;
+      * after any failure the guard stays failed: later calls raise at once, and `abort()` tears the communicator down
+        (NCCL: abort, so that kernels already enqueued do not wait for the missing peer).
+    """
+
+    def __init__(self, group=None, timeout_s=30.0, check_every=64, store=None):
+        self.group, self.timeout_s, self.check_every = group, float(timeout_s), max(1, int(check_every))
+        self.failed, self.step_no, self.pending = None, 0, []
+        self.store = store
+        if store is None and dist.is_initialized() and dist.get_world_size(group) > 1:
+            try:
+                self.store = dist.distributed_c10d._get_default_store()
+            except Exception:
+                self.store = None
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+
+    def _fail(self, what, cause):
+        self.failed = f"{what}: {cause}"
+        self.abort()
+        raise CollectiveFailure(f"rank {self.rank}: {self.failed}")
+
+    def _check_failed(self):
+        if self.failed:
+            raise CollectiveFailure(f"rank {self.rank}: {self.failed} (earlier)")
+
+    def leave(self):
+        """Called by a rank that stops taking part, between steps, with none of its kernels or collectives in flight."""
+        if self.store is not None:
+            self.store.add("ds41_b200/left", 1)
+
+    def before_step(self):
+        self._check_failed()
+        self.step_no += 1
+        if self.store is not None and self.world > 1 and self.step_no % self.check_every == 1 % self.check_every:
+            try:
+                left = self.store.add("ds41_b200/left", 0)
+            except Exception as exc:  # the store lives on rank 0: gone means rank 0 is gone
+                self._fail("rendezvous store", exc)
+            if left:
+                self._fail("before launch", f"{left} rank(s) left the group")
+
+    def collective(self, what, issue):
+        """issue() starts the collective with async_op=True and returns its work handle."""
+        import datetime
+        self._check_failed()
+        try:
+            work = issue()
+        except Exception as exc:
+            self._fail(what, exc)
+        if work is None:
+            return
+        on_device = torch.cuda.is_available() and dist.get_backend(self.group) == "nccl"
+        try:
+            if on_device:
+                work.wait()  # orders the current stream after the collective; the host does not block
+                if torch.cuda.is_current_stream_capturing():
+                    return   # part of a CUDA graph: there is no per-replay handle; finish() bounds the replay's wait
+                self.pending.append((what, work))
+                if len(self.pending) > 64:
+                    self.pending = [(w, h) for w, h in self.pending if not h.is_completed()][-64:]
+            else:
+                work.wait(datetime.timedelta(seconds=self.timeout_s))
+        except Exception as exc:
+            self._fail(what, exc)
+
+    def finish(self):
+        """Waits, with the time limit, for everything enqueued on the current stream, then surfaces recorded errors."""
+        import time
+        self._check_failed()
+        if torch.cuda.is_available():
+            done = torch.cuda.Event()
+            done.record()
+            deadline = time.monotonic() + self.timeout_s
+            spins = 0
+            while not done.query():
+                spins += 1
+                if spins > 2000:
+                    time.sleep(0.0002)
+                if time.monotonic() > deadline:
+                    names = ", ".join(w for w, h in self.pending if not h.is_completed()) or "kernels"
+                    self._fail("step did not finish", f"no completion within {self.timeout_s:g} s (pending: {names})")
+        for what, work in self.pending:
+            exc = work.exception() if work.is_completed() else None
+            if exc is not None:
+                self.pending = []
+                self._fail(what, exc)
+        self.pending = []
+
+    def abort(self):
+        if not dist.is_initialized():
+            return
+        try:
+            if dist.get_backend(self.group) == "nccl":
+                dist.distributed_c10d._abort_process_group(self.group)
+        except Exception:
+            pass
+
+
 def shard_plan(vocab, world, block=128):
     """[(offset, length)] per rank: contiguous ranges on `block` boundaries, the first ranks take the extra blocks."""
     blocks = (vocab + block - 1) // block
@@ -62,8 +177,9 @@ class ShardedSampler:
     launches_per_step = 2
 
     def __init__(self, pkg, torch_mod, device, rows, vocab_offset, vocab_local, vocab, temperature, top_p, group=None,
-                 world=None):
+                 world=None, guard=None):
         self.pkg, self.device, self.rows = pkg, device, rows
+        self.guard = guard or StepGuard(group)
         self.v0, self.vn, self.vocab = vocab_offset, vocab_local, vocab
         self.t, self.top_p, self.group = temperature, top_p, group
         self.world = world or (dist.get_world_size(group) if dist.is_initialized() else 1)
@@ -105,7 +221,8 @@ class ShardedSampler:
         """logits: this rank's [rows, vocab_local] slice.  Every rank ends with the same tokens / status."""
         self.candidates(logits)
         if self.world > 1:
-            dist.all_gather_into_tensor(self.gathered, self.local, group=self.group)
+            self.guard.collective("candidate all-gather", lambda: dist.all_gather_into_tensor(
+                self.gathered, self.local, group=self.group, async_op=True))
         else:
             self.gathered.copy_(self.local)
         self.combine(seeds, steps, tokens, status, slot, purpose)
@@ -126,7 +243,8 @@ class ShardedSampler:
         mine[:, : self.vn] = logits[rows]
         everyone = torch.empty((self.world, n, width), dtype=torch.float32, device=self.device)
         if self.world > 1:
-            dist.all_gather_into_tensor(everyone.view(-1), mine.view(-1), group=self.group)
+            self.guard.collective("uncovered-row all-gather", lambda: dist.all_gather_into_tensor(
+                everyone.view(-1), mine.view(-1), group=self.group, async_op=True))
         else:
             everyone[0] = mine
         full = torch.cat([everyone[r, :, :length] for r, (_, length) in enumerate(plan)], dim=1).contiguous()
@@ -159,8 +277,9 @@ class PeerMappingUnavailable(RuntimeError):
 class RowExchange:
     """One peer-visible full-vocabulary logits buffer [rows_per_owner, vocab] per rank, mapped into every rank."""
 
-    def __init__(self, pkg, device, rows, vocab, group=None):
+    def __init__(self, pkg, device, rows, vocab, group=None, guard=None):
         self.pkg, self.device, self.rows, self.vocab, self.group = pkg, device, rows, vocab, group
+        self.guard = guard or StepGuard(group)
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.rows_per_owner, plan = rows_plan(rows, self.world)
@@ -243,7 +362,8 @@ class RowExchange:
     def writers_done(self):
         """Stream-ordered: returns (on the stream) once every rank's head kernel has finished its peer stores."""
         if self.world > 1:
-            dist.all_reduce(self.word, group=self.group)
+            self.guard.collective("writers-done all-reduce", lambda: dist.all_reduce(self.word, group=self.group,
+                                                                                      async_op=True))
 
     def sample_mine(self, temperature, top_p, seeds, steps, slot=0, purpose=0, **kw):
         n = self.my_rows
@@ -256,7 +376,8 @@ class RowExchange:
     def publish(self, tokens, status):
         """All-gather of every owner's (tokens, status); also orders the next step's writers after this step's readers."""
         if self.world > 1:
-            dist.all_gather_into_tensor(self.everyone.view(-1), self.packed.view(-1), group=self.group)
+            self.guard.collective("token all-gather", lambda: dist.all_gather_into_tensor(
+                self.everyone.view(-1), self.packed.view(-1), group=self.group, async_op=True))
         else:
             self.everyone[0] = self.packed
         if self.rows == self.world * self.rows_per_owner and tokens.is_contiguous() and status.is_contiguous():
@@ -284,20 +405,22 @@ class ShardedDecodeTail:
     `probe_every` steps whenever more than a quarter of the rows of a step were not covered."""
 
     def __init__(self, pkg, device, rows, vocab_offset, vocab_local, vocab, temperature, top_p, strategy="auto",
-                 group=None, probe_every=256):
+                 group=None, probe_every=256, timeout_s=30.0):
         self.pkg, self.device, self.rows, self.v0, self.vn, self.vocab = pkg, device, rows, vocab_offset, vocab_local, vocab
+        self.guard = StepGuard(group, timeout_s)
         self.t, self.top_p, self.strategy, self.probe_every = temperature, top_p, strategy, probe_every
         self.rows_mode_left = 0
         self.exchange, self.exchange_error = None, None
         if strategy != "candidates":
             try:
-                self.exchange = RowExchange(pkg, device, rows, vocab, group)
+                self.exchange = RowExchange(pkg, device, rows, vocab, group, self.guard)
             except PeerMappingUnavailable as exc:  # the same on every rank: fall back to the NCCL-only exchange
                 self.exchange_error = str(exc)
                 self.strategy = strategy = "candidates"
         self.cands = None
         if strategy != "rows":
-            self.cands = ShardedSampler(pkg, torch, device, rows, vocab_offset, vocab_local, vocab, temperature, top_p, group)
+            self.cands = ShardedSampler(pkg, torch, device, rows, vocab_offset, vocab_local, vocab, temperature, top_p, group,
+                                        guard=self.guard)
             self.local_logits = torch.empty((rows, vocab_local), dtype=torch.float32, device=device)
         self.steps_rows = self.steps_candidates = 0
 
@@ -307,6 +430,9 @@ class ShardedDecodeTail:
         return "rows" if self.rows_mode_left > 0 else "candidates"
 
     def step(self, a, a_scale, w, w_scale, seeds, steps, tokens, status, error_flag=None, slot=0, purpose=0):
+        """Enqueues one step.  `self.guard.finish()` is the bounded wait for it (and where a failed collective
+        surfaces as CollectiveFailure); call it wherever the host would otherwise synchronise."""
+        self.guard.before_step()
         if self.mode() == "rows":
             ex = self.exchange
             ex.head_scatter(a, a_scale, w, w_scale, self.v0, error_flag)

@@ -306,7 +306,7 @@ int ds41_b200_peer_free(void *ptr);
  * (:450-461, :603-612).  top ids and top1 are exact; logsumexp and the log-probabilities agree with the reference's
  * sequential FP64 sum to a few units in the last place (relative 1e-13 is the tested tolerance).  Rows with a
  * non-finite logit get status DS41_B200_ROW_NONFINITE, NaN values and ids -1.  The logits_sha256 fingerprint of the
- * same event is not computed here. */
+ * same event comes from ds41_b200_logits_sha256 below. */
 #define DS41_B200_SCORE_MAX_TOP 32
 typedef struct ds41_b200_score_args {
   uint32_t struct_bytes;
@@ -321,6 +321,11 @@ typedef struct ds41_b200_score_args {
   int32_t *status;        /* [rows] out */
 } ds41_b200_score_args;
 int ds41_b200_score_logits(const ds41_b200_score_args *args, cudaStream_t stream);
+/* digests[r, 0..32) = SHA-256 of row r's fp32 logits in little-endian byte order: the logits_sha256 field of the
+ * reference's score event (engine/src/server.cpp:184-197), computed where the row lies, so that 32 bytes per row leave
+ * the device instead of the row.  One thread per row (a hash is a chain): milliseconds per full-vocabulary row. */
+int ds41_b200_logits_sha256(const float *logits, int rows, int vocab, int64_t logits_stride, uint8_t *digests,
+                            cudaStream_t stream);
 
 /* ---- test hook ---------------------------------------------------------------------------------------------------
  * out[i] = the samplers' own exp(x[i]) for x <= 0 (device pointers), so that its error can be measured against a

@@ -43,3 +43,17 @@ def test_score_rejects_nonfinite_rows_and_bad_arguments(pkg, oracle):
     assert np.isnan(lse.cpu().numpy()[1]) and (ids.cpu().numpy()[1] == -1).all() and top1.cpu().numpy()[1] == -1
     with pytest.raises(RuntimeError):
         pkg.score_logits(torch.from_numpy(x).cuda(), 33)
+
+
+@pytest.mark.parametrize("vocab", [1, 13, 14, 15, 16, 17, 129280, 129281])
+def test_logits_sha256(pkg, vocab):
+    """engine/src/server.cpp:184-197: SHA-256 over the row's fp32 values in little-endian byte order (all padding cases
+    of the last block: 0..15 left-over words)."""
+    import hashlib
+    rows = 5
+    g = torch.Generator(device="cuda").manual_seed(vocab)
+    buf = torch.randn(rows, vocab + 3, device="cuda", generator=g)
+    x = buf[:, :vocab]
+    got = pkg.logits_sha256(x)
+    want = [hashlib.sha256(r.tobytes()).hexdigest() for r in x.cpu().numpy()]
+    assert got == want

@@ -166,6 +166,7 @@ def rows_worker(rank, world, port, out, rows=7):
     want, wst = orc.sample_rows(x, 0.8, 0.9, seeds, steps, threads=2)
     ex = sh.RowExchange.__new__(sh.RowExchange)     # no peer memory on CPU: only the host logic is under test
     ex.world, ex.rank, ex.rows, ex.vocab, ex.group, ex.device = world, rank, rows, vocab, None, torch.device("cpu")
+    ex.guard = sh.StepGuard(None)
     ex.rows_per_owner, plan = sh.rows_plan(rows, world)
     ex.row0, ex.my_rows = plan[rank]
     ex.packed = torch.full((2, ex.rows_per_owner), -1, dtype=torch.int32)
@@ -202,3 +203,101 @@ def test_three_rank_row_exchange_on_gloo(rows):
         assert len(out) == world
         for rank in range(world):
             assert out[rank] == [], out[rank]
+
+
+def _failure_rank_setup(rank, world, port, timeout_s, check_every):
+    sys.path.insert(0, ROOT)
+    import __graft_entry__ as entry
+    entry.load_package()
+    sh = importlib.import_module("ds41_b200.sharded")
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    rows = 6
+    guard = sh.StepGuard(None, timeout_s=timeout_s, check_every=check_every)
+    ex = sh.RowExchange.__new__(sh.RowExchange)     # host logic only: no peer memory on CPU
+    ex.world, ex.rank, ex.rows, ex.vocab, ex.group, ex.device = world, rank, rows, 128, None, torch.device("cpu")
+    ex.guard = guard
+    ex.rows_per_owner, plan = sh.rows_plan(rows, world)
+    ex.row0, ex.my_rows = plan[rank]
+    ex.packed = torch.full((2, ex.rows_per_owner), rank, dtype=torch.int32)
+    ex.everyone = torch.empty((world, 2, ex.rows_per_owner), dtype=torch.int32)
+    ex.word = torch.zeros(1, dtype=torch.int32)
+    return sh, guard, ex, rows
+
+
+def _one_step(guard, ex, rows):
+    guard.before_step()
+    ex.writers_done()
+    tokens, status = torch.empty(rows, dtype=torch.int32), torch.empty(rows, dtype=torch.int32)
+    ex.publish(tokens, status)
+    guard.finish()
+    return tokens
+
+
+def never_arrives_worker(rank, world, port, out):
+    """Rank 1 takes part in one step and then never enters the next one's collectives (it is stuck on the host)."""
+    import time
+    sh, guard, ex, rows = _failure_rank_setup(rank, world, port, timeout_s=2.0, check_every=1000)
+    tokens = _one_step(guard, ex, rows)
+    report = {"first_step_ok": tokens.tolist() == [0, 0, 0, 1, 1, 1]}
+    if rank == 1:
+        time.sleep(6.0)                     # longer than the survivor's limit; it leaves without a word
+        out[rank] = report
+        return
+    t0 = time.monotonic()
+    try:
+        _one_step(guard, ex, rows)
+        report["raised"] = None
+    except sh.CollectiveFailure as exc:
+        report["raised"], report["seconds"] = str(exc), time.monotonic() - t0
+    try:                                     # the guard stays failed: nothing is launched into a broken group
+        guard.before_step()
+        report["stays_failed"] = False
+    except sh.CollectiveFailure:
+        report["stays_failed"] = True
+    out[rank] = report
+
+
+def test_rank_that_never_arrives_ends_in_a_clean_error_on_gloo():
+    world, port = 2, 33500 + os.getpid() % 2000
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(never_arrives_worker, args=(world, port, out), nprocs=world, join=True)
+        survivor = out[0]
+        assert survivor["first_step_ok"] and out[1]["first_step_ok"]
+        assert survivor["raised"] and "writers-done all-reduce" in survivor["raised"], survivor
+        assert survivor["seconds"] < 5.0, survivor       # the 2 s limit, not the process group's default 30 minutes
+        assert survivor["stays_failed"]
+
+
+def leaves_worker(rank, world, port, out):
+    """Rank 2 leaves between steps and says so in the store; both survivors stop with the same clean error."""
+    import time
+    sh, guard, ex, rows = _failure_rank_setup(rank, world, port, timeout_s=2.0, check_every=1)
+    _one_step(guard, ex, rows)
+    if rank == 2:
+        guard.leave()                        # nothing of this rank is in flight: the step above has finished
+        out[rank] = {"left": True}
+        time.sleep(1.0)
+        return
+    report = {"raised": None, "steps_after": 0}
+    for _ in range(400):
+        try:
+            guard.before_step()              # the survivors' check before their next launch
+        except sh.CollectiveFailure as exc:
+            report["raised"] = str(exc)
+            break
+        report["steps_after"] += 1           # not yet visible: this step launches nothing here (the peer may be gone)
+        time.sleep(0.005)
+    out[rank] = report
+    if rank == 0:
+        time.sleep(1.5)                      # rank 0 hosts the store: keep it up until the others have read it
+
+
+def test_rank_that_leaves_between_steps_stops_the_others_before_their_next_launch_on_gloo():
+    world, port = 3, 35500 + os.getpid() % 2000
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(leaves_worker, args=(world, port, out), nprocs=world, join=True)
+        assert out[2] == {"left": True}
+        for rank in (0, 1):
+            assert out[rank]["raised"] and "left the group" in out[rank]["raised"], out[rank]
