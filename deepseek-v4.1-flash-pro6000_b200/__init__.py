@@ -381,6 +381,28 @@ def score_logits(logits, top_n=0):
     return lse, top1, ids, lp, status
 
 
+SAMPLER_PHASES = ("flat_stats_kernel", "flat_hist_kernel", "flat_window_kernel", "flat_mass_kernel",
+                  "flat_resolve_kernel", "row_kernel", "replay_sample_kernel")
+
+
+def profile_sampler_call(call):
+    """Runs call() (one sample_logits on the batch path) with the library's phase events on and returns
+    {kernel name: milliseconds}, timed with CUDA events on the launching stream."""
+    L = lib()
+    L.ds41_b200_profile_phases.argtypes = [C.c_int]
+    L.ds41_b200_profile_read.argtypes = [C.POINTER(C.c_float), C.c_int]
+    _check(L.ds41_b200_profile_phases(1), "ds41_b200_profile_phases")
+    try:
+        call()
+        ms = (C.c_float * len(SAMPLER_PHASES))()
+        n = L.ds41_b200_profile_read(ms, len(SAMPLER_PHASES))
+        if n < 0:
+            raise RuntimeError("ds41_b200_profile_read failed")
+        return {SAMPLER_PHASES[i]: float(ms[i]) for i in range(n)}
+    finally:
+        L.ds41_b200_profile_phases(0)
+
+
 def logits_sha256(logits):
     """SHA-256 of every row's fp32 logits (the logits_sha256 of the reference's score event, server.cpp:184-197), as
     hexadecimal strings."""

@@ -20,6 +20,7 @@
 #include "flat.cuh"
 
 #include "row_core.cuh"
+#include "phase_events.h"
 
 namespace ds41 {
 namespace {
@@ -593,7 +594,10 @@ __global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
       e[i] = r < n ? exp_nonpos((double(ys[i]) - m64) * inv_t) : 0.0;
     }
     const double through0 = mass_before + flat_prefix2(red, e[0], e[1]), through1 = through0 + e[1];
-    const double rel = 2.0 * (double(a.vocab) + kFlatWeightUlps) * kU * a.bound_scale;
+    // The reference's test is chain(p_i, i <= k) >= top with p_i = w_i / chain(w, all n ids): its two chains round by at
+    // most (k - 1) and (n - 1) units, k <= the ids above the window plus the window's; the sums here add a few hundred.
+    const double k_bound = fmin(double(a.vocab), double(info.n_before) + double(n));
+    const double rel = (k_bound + double(a.vocab) + 2.0 * kFlatWeightUlps + 512.0) * kU * a.bound_scale;
     const double target_p = a.top_p * z, lo = target_p * (1.0 - rel), hi = target_p * (1.0 + rel);
     if (tid == 0) { found_at = 0x7fffffff; cut_amb = 0; }
     __syncthreads();
@@ -620,7 +624,7 @@ __global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
       for (int i = 0; i < 2; ++i)
         if (2 * tid + i <= pos) atomicAdd(&ksum[ids[i] / kFlatSub], e[i]);
       cut = Cut{cut_y, cut_id};
-      kept = a.vocab;  // (an upper bound is all the draw's slack needs)
+      kept = min(a.vocab, info.n_before + pos + 1);  // ids with weight in the draw: those above the window and the window's up to the cut
       status = cut_amb ? 2 : 0;  // inside the FP64 bound: decided, flagged like every other path does
     }
     __syncthreads();
@@ -757,15 +761,22 @@ cudaError_t launch_flat(FlatArgs a, void *scratch, cudaStream_t stream) {
   const size_t zeroed = 4 * sizeof(int) + rows * 4 * sizeof(int) + (parts > 1 && !full ? rows * kFlatBins * sizeof(unsigned long long) : 0);
   cudaError_t e = cudaMemsetAsync(scratch, 0, zeroed, stream);
   if (e != cudaSuccess) return e;
+  phase_restart();
+  phase_mark(stream);
   if (!a.head_stats) flat_stats_kernel<<<a.rows * parts, kFT, 0, stream>>>(a);
+  phase_mark(stream);
   if (!full) flat_hist_kernel<<<a.rows * parts, kFT, 0, stream>>>(a);
+  phase_mark(stream);
   flat_window_kernel<<<a.rows, kFT, 0, stream>>>(a);
+  phase_mark(stream);
   // the mass pass: eight warps per CTA, one 1024-id sub-region per warp and round
   const int mass_parts = a.rows >= 64 ? 4 : 16;
   FlatArgs m = a;
   m.parts = mass_parts;
   flat_mass_kernel<<<a.rows * mass_parts, kFlatMassThreads, 0, stream>>>(m);
+  phase_mark(stream);
   flat_resolve_kernel<<<a.rows, kFT, 0, stream>>>(a);
+  phase_mark(stream);
   return cudaGetLastError();
 }
 

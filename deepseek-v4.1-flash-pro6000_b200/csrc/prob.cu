@@ -69,6 +69,7 @@ struct ProbArgs {
 
 __global__ void __launch_bounds__(kRT) probabilities_kernel(ProbArgs a) {
   __shared__ ReplaySmem s;
+  extern __shared__ __align__(16) unsigned char dynamic[];
   unsigned char *mine = a.scratch + size_t(blockIdx.x) * size_t(kReplayPad) * 12;
   unsigned long long *key = reinterpret_cast<unsigned long long *>(mine);
   int *idx = reinterpret_cast<int *>(mine + size_t(kReplayPad) * 8);
@@ -89,7 +90,7 @@ __global__ void __launch_bounds__(kRT) probabilities_kernel(ProbArgs a) {
       const int b = first_max(s, x, a.vocab);
       for (int i = threadIdx.x; i < a.vocab; i += kRT) p[i] = i == b ? 1.0 : 0.0;
     } else {
-      replay_probabilities(s, x, a.vocab, a.t, a.top_p, p, key, idx);
+      replay_probabilities(s, x, a.vocab, a.t, a.top_p, p, key, idx, dynamic);
     }
     if (threadIdx.x == 0) a.status[row] = 0;
     __syncthreads();
@@ -272,7 +273,10 @@ extern "C" int ds41_b200_probabilities(const ds41_b200_prob_args *p, cudaStream_
              p->temperature > 0 ? std::fmax(p->temperature, 1e-5) : 0.0,  // engine/src/sampling.cpp:209-210
              p->top_p, p->probabilities, p->status, static_cast<unsigned char *>(p->scratch)};
   const int ctas = int(need / (size_t(kReplayPad) * 12));
-  probabilities_kernel<<<ctas, kRT, 0, stream>>>(a);
+  const cudaError_t e = cudaFuncSetAttribute(probabilities_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             int(kReplayDynamicBytes));
+  if (e != cudaSuccess) return int(e);
+  probabilities_kernel<<<ctas, kRT, kReplayDynamicBytes, stream>>>(a);
   return int(cudaGetLastError());
 }
 

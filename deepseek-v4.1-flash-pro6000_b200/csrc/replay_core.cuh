@@ -13,9 +13,10 @@ constexpr int kRT = kReplayThreads;
 constexpr int kTile = 2048;   // elements sorted / summed out of shared memory at a time
 
 struct ReplaySmem {
+  double stage[kTile];
   unsigned long long key[kTile];
   int idx[kTile];
-  double stage[kTile];
+  unsigned long long scan[kRT / 32];
   float red_f[kRT / 32];
   int red_i[kRT / 32];
   double bcast_d[4];
@@ -34,7 +35,7 @@ __device__ void sort_pairs(ReplaySmem &s, unsigned long long *key, int *idx) {
   auto local_stages = [&](int base, int k, int j_first) {  // strides j_first, j_first / 2 ... 1 of merge step k
     for (int jj = j_first; jj > 0; jj >>= 1) {
       for (int i = tid; i < kTile / 2; i += kRT) {
-        const int lo = 2 * jj * (i / jj) + (i % jj), hi = lo + jj;
+        const int lo = ((i & ~(jj - 1)) << 1) | (i & (jj - 1)), hi = lo + jj;   // jj is a power of two
         const bool up = ((base + lo) & k) == 0;
         const unsigned long long ka = s.key[lo], kb = s.key[hi];
         const int ia = s.idx[lo], ib = s.idx[hi];
@@ -53,7 +54,7 @@ __device__ void sort_pairs(ReplaySmem &s, unsigned long long *key, int *idx) {
   for (int k = 2 * kTile; k <= kReplayPad; k <<= 1) {
     for (int j = k >> 1; j >= kTile; j >>= 1) {  // partners further apart than a tile
       for (int i = tid; i < kReplayPad / 2; i += kRT) {
-        const int lo = 2 * j * (i / j) + (i % j), hi = lo + j;
+        const int lo = ((i & ~(j - 1)) << 1) | (i & (j - 1)), hi = lo + j;
         const bool up = (lo & k) == 0;
         const unsigned long long ka = key[lo], kb = key[hi];
         const int ia = idx[lo], ib = idx[hi];
@@ -71,25 +72,334 @@ __device__ void sort_pairs(ReplaySmem &s, unsigned long long *key, int *idx) {
   }
 }
 
-// sum of value(0) .. value(n-1) in index order, on one thread (tiles staged through shared memory by all threads);
-// returned to every thread
-template <class Value>
-__device__ double sequential_sum(ReplaySmem &s, int n, Value value) {
-  double acc = 0;
-  for (int base = 0; base < n; base += kTile) {
-    const int m = min(kTile, n - base);
-    for (int i = threadIdx.x; i < m; i += kRT) s.stage[i] = value(base + i);
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      for (int i = 0; i < m; ++i) acc += s.stage[i];
+// ---------------------------------------------------------------------------------------------------------------
+// The reference's loops `acc += v[i]` run on one host thread; what has to be reproduced is every rounding of that
+// chain.  For non-negative terms the chain can be followed exactly in parallel.  While acc stays inside one binade
+// [2^e, 2^(e+1)) its grid has the fixed spacing U = 2^(e-52), acc = S * U with an integer S, and
+//     fl(acc + x) = (S + rn(x / U)) * U
+// where rn rounds to the nearest integer: the rounding of the sum does not depend on S, except when x / U lies exactly
+// half way between two integers (the tie goes to the even S + ...).  So inside a binade the chain is an INTEGER prefix
+// sum of rn(x_i / U), which a block scan computes exactly, and every intermediate acc is known exactly.  The two events
+// that end such a stretch are found by the same scan: the first term whose sum reaches 2^(e+1) (the spacing changes) and
+// the first tie.  That one term is added with a real FP64 addition to the exactly known acc before it (this IS the
+// reference's operation), and the scan restarts behind it with the new acc.  A whole pass costs one block scan per tile
+// plus one per binade crossed (a few dozen), instead of one dependent addition per term on a single thread.
+// Terms that are negative, NaN or infinite (rows a caller passed in without validation) take the literal loop.
+constexpr int kSumPer = 4;                 // consecutive terms a thread holds in registers
+constexpr int kSumTile = kSumPer * kRT;    // terms scanned at a time
+constexpr unsigned long long kTwo52 = 1ull << 52, kTwo53 = 1ull << 53;
+
+struct SeqResult {
+  int found;            // index of the term after which stop(acc) first held; -1: the loop ran through
+  double acc, before;   // acc after that term (or after the last one) and just before it
+};
+
+// x = m * 2^(be - 1075), be >= 1 (subnormals: be = 1 without the implicit bit)
+__device__ __forceinline__ void split_double(double x, int &be, unsigned long long &m) {
+  const unsigned long long b = (unsigned long long)__double_as_longlong(x);
+  be = int(b >> 52) & 0x7ff;
+  m = b & (kTwo52 - 1);
+  if (be) m |= kTwo52; else be = 1;
+}
+
+// units * 2^(be - 1075) for units < 2^53 (below 2^52 only in the subnormal range, be == 1)
+__device__ __forceinline__ double join_double(unsigned long long units, int be) {
+  return __longlong_as_double((long long)(units >= kTwo52 ? ((unsigned long long)be << 52) + (units - kTwo52) : units));
+}
+
+// rn(x / U) for U = 2^(be_acc - 1075), x >= 0 finite; *tie: x / U is exactly half way (the floor is returned).  Values
+// that certainly carry acc out of its binade are returned as 2^53.
+__device__ __forceinline__ unsigned long long to_units(double x, int be_acc, bool *tie) {
+  int bx;
+  unsigned long long mx;
+  split_double(x, bx, mx);
+  *tie = false;
+  const int shift = be_acc - bx;
+  if (shift <= 0) return shift == 0 ? mx : (mx ? kTwo53 : 0ull);
+  if (shift >= 64) return 0ull;
+  const unsigned long long q = mx >> shift, rem = mx & ((1ull << shift) - 1), half = 1ull << (shift - 1);
+  if (rem == half) *tie = true;
+  return q + (rem > half ? 1ull : 0ull);
+}
+
+// exclusive prefix of one value per thread over the block, in thread order; *total = the block's sum (mod 2^64)
+__device__ __forceinline__ unsigned long long block_exclusive_u64(ReplaySmem &s, unsigned long long v,
+                                                                  unsigned long long *total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned long long inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long up = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += up;
+  }
+  if (lane == 31) s.scan[warp] = inc;
+  __syncthreads();
+  unsigned long long w = lane < kRT / 32 ? s.scan[lane] : 0ull, winc = w;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long up = __shfl_up_sync(0xffffffffu, winc, o);
+    if (lane >= o) winc += up;
+  }
+  *total = __shfl_sync(0xffffffffu, winc, 31);
+  const unsigned long long before_warp = __shfl_sync(0xffffffffu, winc - w, warp);
+  __syncthreads();   // scan[] may be rewritten by the next call
+  return before_warp + inc - v;
+}
+
+// acc = 0; for i in [0, n): acc += value(i); if (stop(acc)) return i   -- with every rounding of that chain.
+// stop must be monotone (once true it stays true as acc grows) and may be false throughout.
+// (first, acc0): the loop resumed at term `first` with the acc the earlier terms left.
+template <class Value, class Stop>
+__device__ SeqResult exact_sequential(ReplaySmem &s, int n, Value value, Stop stop, int first = 0, double acc0 = 0.0) {
+  const int tid = threadIdx.x;
+  double acc = acc0;         // the same in every thread
+  for (int base = first; base < n; base += kSumTile) {
+    const int m = min(kSumTile, n - base);
+    // every thread keeps kSumPer consecutive terms in registers
+    double v[kSumPer];
+    int bad = 0;
+#pragma unroll
+    for (int r = 0; r < kSumPer; ++r) {
+      const int i = tid * kSumPer + r;
+      v[r] = i < m ? value(base + i) : 0.0;
+      bad |= !(v[r] >= 0.0 && v[r] < CUDART_INF);
+    }
+    if (tid == 0) { s.bcast_i[0] = 0x7fffffff; s.bcast_i[1] = 0x7fffffff; }
+    bad = __syncthreads_or(bad);
+    if (bad) {   // the literal loop, one thread
+      if (tid == 0) {
+        int found = -1;
+        double before = acc;
+        for (int i = 0; i < m; ++i) {
+          before = acc;
+          acc += value(base + i);
+          if (stop(acc)) { found = base + i; break; }
+        }
+        s.bcast_i[0] = found; s.bcast_d[0] = acc; s.bcast_d[1] = before;
+      }
+      __syncthreads();
+      const int found = s.bcast_i[0];
+      acc = s.bcast_d[0];
+      const double before = s.bcast_d[1];
+      __syncthreads();
+      if (found >= 0) return SeqResult{found, acc, before};
+      continue;
+    }
+    int pos = 0;
+    while (pos < m) {   // uniform: one pass per stretch of the chain inside one binade
+      int be;
+      unsigned long long s0;
+      split_double(acc, be, s0);
+      unsigned long long t[kSumPer], sum = 0;
+      unsigned ties = 0;
+#pragma unroll
+      for (int r = 0; r < kSumPer; ++r) {
+        const int i = tid * kSumPer + r;
+        bool tie = false;
+        t[r] = (i >= pos && i < m) ? to_units(v[r], be, &tie) : 0ull;
+        ties |= tie ? (1u << r) : 0u;
+        sum += t[r];
+      }
+      unsigned long long total;
+      unsigned long long running = s0 + block_exclusive_u64(s, sum, &total);
+      int special = 0x7fffffff, stop_at = 0x7fffffff;
+      double at_acc = 0.0, at_before = 0.0, special_term = 0.0;
+      unsigned long long special_before = 0;
+      // the chain is monotone: only a thread whose last term crosses a line has to look at its terms one by one
+      const unsigned long long after_mine = running + sum;
+      const bool look = ties != 0 || after_mine >= kTwo53 || (tid * kSumPer < m && stop(join_double(after_mine, be)));
+      if (look) {
+#pragma unroll
+        for (int r = 0; r < kSumPer; ++r) {
+          const int i = tid * kSumPer + r;
+          if (i < pos || i >= m || special != 0x7fffffff || stop_at != 0x7fffffff) continue;
+          const unsigned long long units_before = running;
+          running += t[r];
+          if (((ties >> r) & 1u) || running >= kTwo53) {
+            special = i; special_before = units_before; special_term = v[r];
+          } else {
+            const double a = join_double(running, be);
+            if (stop(a)) { stop_at = i; at_acc = a; at_before = join_double(units_before, be); }
+          }
+        }
+      }
+      if (special != 0x7fffffff) atomicMin(&s.bcast_i[0], special);
+      if (stop_at != 0x7fffffff) atomicMin(&s.bcast_i[1], stop_at);
+      __syncthreads();
+      const int js = s.bcast_i[0], jt = s.bcast_i[1];
+      if (jt < js) {   // the loop stops inside this stretch
+        if (stop_at == jt) { s.bcast_d[0] = at_acc; s.bcast_d[1] = at_before; }
+        __syncthreads();
+        const SeqResult out{base + jt, s.bcast_d[0], s.bcast_d[1]};
+        __syncthreads();
+        return out;
+      }
+      if (js == 0x7fffffff) {   // the rest of the tile stays inside the binade
+        acc = join_double(s0 + total, be);
+        break;
+      }
+      if (special == js) {      // the term that leaves the binade (or ties): the reference's own addition
+        const double before = join_double(special_before, be);
+        s.bcast_d[1] = before;
+        s.bcast_d[0] = __dadd_rn(before, special_term);
+      }
+      __syncthreads();
+      acc = s.bcast_d[0];
+      const double before = s.bcast_d[1];
+      if (tid == 0) { s.bcast_i[0] = 0x7fffffff; s.bcast_i[1] = 0x7fffffff; }
+      __syncthreads();   // (also orders the reset before the next round's minima, which follow the scan's barriers)
+      if (stop(acc)) return SeqResult{base + js, acc, before};
+      pos = js + 1;
     }
     __syncthreads();
   }
-  if (threadIdx.x == 0) s.bcast_d[0] = acc;
+  return SeqResult{-1, acc, acc};
+}
+
+template <class Value>
+__device__ double sequential_sum(ReplaySmem &s, int n, Value value) {
+  return exact_sequential(s, n, value, [](double) { return false; }).acc;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Order of the probabilities (p descending, id ascending) without a full sort: the ids are distributed over kBuckets
+// ranges of the upper key word (one pass of counting, one of scattering), and a bucket is put in order only when the
+// top-p loop is about to reach it (one warp per bucket out of its own shared-memory area; the whole CTA for a bucket of
+// up to kTile entries).  The loop normally stops long before the tail, so most buckets are never ordered.
+constexpr int kBuckets = 4096;
+constexpr int kWarpSort = 256;                       // entries a warp orders out of its own area
+constexpr int kSpanCap = 96 << 20;                   // binades (2^20 upper-word steps each) the bucket grid covers
+constexpr size_t kReplayDynamicBytes = size_t(kRT / 32) * kWarpSort * 12 + size_t(kBuckets + 1) * 4;
+
+struct BucketOrder {
+  int *starts;                 // [kBuckets + 1] first position of each bucket (dynamic shared memory)
+  unsigned long long *wkey;    // [warps][kWarpSort]
+  int *widx;
+  int next_bucket, ordered;    // buckets before next_bucket are in order: positions [0, ordered)
+};
+
+__device__ __forceinline__ BucketOrder bucket_areas(unsigned char *dynamic) {
+  BucketOrder b;
+  b.wkey = reinterpret_cast<unsigned long long *>(dynamic);
+  b.widx = reinterpret_cast<int *>(dynamic + size_t(kRT / 32) * kWarpSort * 8);
+  b.starts = reinterpret_cast<int *>(dynamic + size_t(kRT / 32) * kWarpSort * 12);
+  b.next_bucket = 0; b.ordered = 0;
+  return b;
+}
+
+// Distributes (key, id) of p[0..n) into key[] / idx[] by bucket.  p_max / p_low = (about) the largest and smallest p.
+__device__ void bucket_scatter(ReplaySmem &s, BucketOrder &b, const double *p, int n, double p_max, double p_low,
+                               unsigned long long *key, int *idx) {
+  const int tid = threadIdx.x;
+  // the grid runs from the largest p to the smallest (or kSpanCap below the largest; the rest shares the last bucket)
+  const unsigned long long lowest = p_low > 0 ? (unsigned long long)__double_as_longlong(p_low) : ~0ull;
+  const uint32_t hi_min = uint32_t((~(unsigned long long)__double_as_longlong(p_max)) >> 32);
+  const uint32_t hi_low = uint32_t((~lowest) >> 32);
+  uint32_t span = lowest == ~0ull ? uint32_t(kSpanCap) : (hi_low >= hi_min ? hi_low - hi_min + 1 : 1);
+  if (span > uint32_t(kSpanCap)) span = kSpanCap;
+  const float scale = float(kBuckets - 1) / float(span);
+  auto bucket_of = [hi_min, scale](unsigned long long k) {
+    const uint32_t hi = uint32_t(k >> 32), d = hi > hi_min ? hi - hi_min : 0u;
+    const float f = __uint2float_rz(d) * scale;   // monotone in the key
+    return f >= float(kBuckets - 1) ? kBuckets - 1 : int(f);
+  };
+  int *count = b.starts, *cursor = reinterpret_cast<int *>(s.stage);
+  for (int i = tid; i <= kBuckets; i += kRT) count[i] = 0;
   __syncthreads();
-  acc = s.bcast_d[0];
+  for (int i = tid; i < n; i += kRT) atomicAdd(&count[bucket_of(~(unsigned long long)__double_as_longlong(p[i]))], 1);
   __syncthreads();
-  return acc;
+  // exclusive scan of the counts, kBuckets / kRT per thread
+  constexpr int kPerThread = kBuckets / kRT;
+  int mine[kPerThread], sum = 0;
+#pragma unroll
+  for (int r = 0; r < kPerThread; ++r) { mine[r] = count[tid * kPerThread + r]; sum += mine[r]; }
+  unsigned long long total;
+  int at = int(block_exclusive_u64(s, (unsigned long long)sum, &total));
+#pragma unroll
+  for (int r = 0; r < kPerThread; ++r) { count[tid * kPerThread + r] = at; cursor[tid * kPerThread + r] = at; at += mine[r]; }
+  if (tid == 0) count[kBuckets] = n;
+  __syncthreads();
+  for (int i = tid; i < n; i += kRT) {
+    const unsigned long long k = ~(unsigned long long)__double_as_longlong(p[i]);
+    const int pos = atomicAdd(&cursor[bucket_of(k)], 1);
+    key[pos] = k; idx[pos] = i;
+  }
+  __syncthreads();
+  b.next_bucket = 0; b.ordered = 0;
+}
+
+// Puts the next buckets in order until at least `want` more positions are (or every bucket is).  Returns false when a
+// bucket is too large for the shared-memory sorts (rows with long runs of equal logits): the caller sorts the row whole.
+__device__ bool bucket_order_more(ReplaySmem &s, BucketOrder &b, int want, unsigned long long *key, int *idx) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int from = b.next_bucket;
+  int to = from;
+  const int goal = b.ordered + want;
+  while (to < kBuckets && b.starts[to] < goal) ++to;   // uniform: every thread reads the same table
+  if (to == from) return true;
+  bool fits = true;
+  for (int q = from + warp; q < to; q += kRT / 32) {
+    const int st = b.starts[q], m = b.starts[q + 1] - st;
+    if (m <= 1 || m > kWarpSort) continue;
+    unsigned long long *wk = b.wkey + warp * kWarpSort;
+    int *wi = b.widx + warp * kWarpSort;
+    int padded = 2;
+    while (padded < m) padded <<= 1;
+    for (int i = lane; i < padded; i += 32) { wk[i] = i < m ? key[st + i] : ~0ull; wi[i] = i < m ? idx[st + i] : 0x7fffffff; }
+    __syncwarp();
+    for (int k = 2; k <= padded; k <<= 1)
+      for (int jj = k >> 1; jj > 0; jj >>= 1) {
+        for (int i = lane; i < padded / 2; i += 32) {
+          const int lo = ((i & ~(jj - 1)) << 1) | (i & (jj - 1)), hi = lo + jj;   // jj is a power of two
+          const bool up = (lo & k) == 0;
+          const unsigned long long ka = wk[lo], kb = wk[hi];
+          const int ia = wi[lo], ib = wi[hi];
+          if (key_less(kb, ib, ka, ia) == up) { wk[lo] = kb; wk[hi] = ka; wi[lo] = ib; wi[hi] = ia; }
+        }
+        __syncwarp();
+      }
+    for (int i = lane; i < m; i += 32) { key[st + i] = wk[i]; idx[st + i] = wi[i]; }
+    __syncwarp();
+  }
+  __syncthreads();
+  for (int q = from; q < to; ++q) {   // uniform: the buckets that are too large for a warp's area
+    const int st = b.starts[q], m = b.starts[q + 1] - st;
+    if (m <= kWarpSort) continue;
+    if (m > kTile) { fits = false; break; }
+    int padded = kWarpSort * 2;
+    while (padded < m) padded <<= 1;
+    for (int i = tid; i < padded; i += kRT) { s.key[i] = i < m ? key[st + i] : ~0ull; s.idx[i] = i < m ? idx[st + i] : 0x7fffffff; }
+    __syncthreads();
+    for (int k = 2; k <= padded; k <<= 1)
+      for (int jj = k >> 1; jj > 0; jj >>= 1) {
+        for (int i = tid; i < padded / 2; i += kRT) {
+          const int lo = ((i & ~(jj - 1)) << 1) | (i & (jj - 1)), hi = lo + jj;
+          const bool up = (lo & k) == 0;
+          const unsigned long long ka = s.key[lo], kb = s.key[hi];
+          const int ia = s.idx[lo], ib = s.idx[hi];
+          if (key_less(kb, ib, ka, ia) == up) { s.key[lo] = kb; s.key[hi] = ka; s.idx[lo] = ib; s.idx[hi] = ia; }
+        }
+        __syncthreads();
+      }
+    for (int i = tid; i < m; i += kRT) { key[st + i] = s.key[i]; idx[st + i] = s.idx[i]; }
+    __syncthreads();
+  }
+  if (!fits) return false;
+  b.next_bucket = to;
+  b.ordered = b.starts[to];
+  __syncthreads();
+  return true;
+}
+
+// largest value over the block, to every thread
+__device__ float flat_like_max(ReplaySmem &s, float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((threadIdx.x & 31) == 0) s.red_f[threadIdx.x >> 5] = v;
+  __syncthreads();
+  for (int w = 0; w < kRT / 32; ++w) v = fmaxf(v, s.red_f[w]);
+  __syncthreads();
+  return v;
 }
 
 struct Replayed {
@@ -98,16 +408,19 @@ struct Replayed {
 };
 
 // p[0..n) = the reference's probability row of x; key / idx are work space of kReplayPad entries.
+// dynamic: kReplayDynamicBytes of dynamic shared memory for the bucket order (nullptr: the whole row is sorted).
 __device__ Replayed replay_probabilities(ReplaySmem &s, const float *x, int n, double t, double top, double *p,
-                                         unsigned long long *key, int *idx) {
+                                         unsigned long long *key, int *idx, unsigned char *dynamic = nullptr) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // first maximum
-  float best = -CUDART_INF_F;
+  // first maximum (and the minimum: where the bucket grid of the order ends)
+  float best = -CUDART_INF_F, low = CUDART_INF_F;
   int best_id = 0x7fffffff;
   for (int i = tid; i < n; i += kRT) {
     const float v = x[i];
     if (v > best) { best = v; best_id = i; }
+    low = fminf(low, v);
   }
+  low = -flat_like_max(s, -low);
 #pragma unroll
   for (int o = 16; o; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -127,38 +440,43 @@ __device__ Replayed replay_probabilities(ReplaySmem &s, const float *x, int n, d
   for (int i = tid; i < n; i += kRT) p[i] /= z;
   __syncthreads();
   if (top < 1.0) {
-    // order: p descending, id ascending (positive doubles order like their bit patterns)
-    for (int i = tid; i < kReplayPad; i += kRT) {
-      key[i] = i < n ? ~(unsigned long long)__double_as_longlong(p[i]) : ~0ull;
-      idx[i] = i < n ? i : 0x7fffffff;
+    // order: p descending, id ascending (positive doubles order like their bit patterns); mass += p[idx[k++]] while
+    // k < n and mass < top
+    SeqResult c{-1, 0.0, 0.0};
+    bool bucketed = dynamic != nullptr;
+    if (bucketed) {
+      BucketOrder b = bucket_areas(dynamic);
+      bucket_scatter(s, b, p, n, 1.0 / z, exp_nonpos((double(low) - xb) / t) / z, key, idx);
+      int done = 0;
+      while (done < n && c.found < 0) {
+        if (!bucket_order_more(s, b, 2 * kSumTile, key, idx)) { bucketed = false; break; }
+        c = exact_sequential(s, b.ordered, [p, idx](int i) { return p[idx[i]]; },
+                             [top](double mass) { return !(mass < top); }, done, c.acc);
+        done = b.ordered;
+      }
     }
-    __syncthreads();
-    sort_pairs(s, key, idx);
-    // mass += p[idx[k++]] while k < n and mass < top, on one thread
-    double mass = 0, prev = 0;
-    int k = 0;
-    bool done = false;
-    for (int base = 0; base < n && !done; base += kTile) {
-      const int m = min(kTile, n - base);
-      for (int i = tid; i < m; i += kRT) s.stage[i] = p[idx[base + i]];
-      __syncthreads();
-      if (tid == 0) {
-        int i = 0;
-        do { prev = mass; mass += s.stage[i++]; ++k; } while (i < m && k < n && mass < top);
-        s.bcast_i[0] = (k >= n || !(mass < top)) ? 1 : 0;
-        s.bcast_i[1] = k; s.bcast_d[0] = mass; s.bcast_d[1] = prev;
+    if (!bucketed) {
+      for (int i = tid; i < kReplayPad; i += kRT) {
+        key[i] = i < n ? ~(unsigned long long)__double_as_longlong(p[i]) : ~0ull;
+        idx[i] = i < n ? i : 0x7fffffff;
       }
       __syncthreads();
-      done = s.bcast_i[0] != 0;
-      __syncthreads();
+      sort_pairs(s, key, idx);
+      c = exact_sequential(s, n, [p, idx](int i) { return p[idx[i]]; }, [top](double mass) { return !(mass < top); });
     }
-    k = s.bcast_i[1]; mass = s.bcast_d[0]; prev = s.bcast_d[1];
-    __syncthreads();
+    const int k = c.found >= 0 ? c.found + 1 : n;
+    const double mass = c.acc, prev = c.before;
     // how far the crossing is from flipping: the kept prefix reached top by (mass - top), the one before missed it by (top - prev)
     out.cut_margin = k >= n && mass < top ? (top - mass) / top : fmin(mass - top, top - prev) / top;
-    for (int i = k + tid; i < n; i += kRT) p[idx[i]] = 0.0;
+    // the rest is zeroed and every p divided by the kept mass; kept = the order's first k = everything up to the k-th pair
+    const unsigned long long cut_key = key[k - 1];
+    const int cut_id = idx[k - 1];
     __syncthreads();
-    for (int i = tid; i < n; i += kRT) p[i] /= mass;
+    for (int i = tid; i < n; i += kRT) {
+      const double v = p[i];
+      const unsigned long long kk = ~(unsigned long long)__double_as_longlong(v);
+      p[i] = (kk < cut_key || (kk == cut_key && i <= cut_id)) ? v / mass : 0.0;
+    }
     __syncthreads();
   }
   return out;
@@ -173,28 +491,20 @@ __device__ int replay_draw(ReplaySmem &s, int n, double u, Value value, double *
   if (total) *total = z;
   if (!(z > 0)) { *margin = 0.0; return -1; }
   const double target = u * z;
-  double c = 0;
-  int last = -1, found = -1;
-  double c_at = 0, c_before = 0;
-  for (int base = 0; base < n && found < 0; base += kTile) {
-    const int m = min(kTile, n - base);
-    for (int i = threadIdx.x; i < m; i += kRT) s.stage[i] = value(base + i);
+  const SeqResult c = exact_sequential(s, n, value, [target](double acc) { return target < acc; });
+  const int found = c.found;
+  const double c_at = c.acc, c_before = c.before;
+  int last = -1;
+  if (found < 0) {   // the last index with a positive value
+    for (int i = threadIdx.x; i < n; i += kRT)
+      if (value(i) > 0) last = i;
+    if (threadIdx.x == 0) s.bcast_i[0] = -1;
     __syncthreads();
-    if (threadIdx.x == 0) {
-      for (int i = 0; i < m; ++i) {
-        const double before = c;
-        c += s.stage[i];
-        if (s.stage[i] > 0) last = base + i;
-        if (target < c) { found = base + i; c_at = c; c_before = before; break; }
-      }
-      s.bcast_i[0] = found; s.bcast_i[1] = last; s.bcast_d[0] = c_at; s.bcast_d[1] = c_before;
-    }
+    if (last >= 0) atomicMax(&s.bcast_i[0], last);
     __syncthreads();
-    found = s.bcast_i[0];
+    last = s.bcast_i[0];
     __syncthreads();
   }
-  last = s.bcast_i[1]; c_at = s.bcast_d[0]; c_before = s.bcast_d[1];
-  __syncthreads();
   if (found < 0) { *margin = 0.0; return last; }  // rounding left the target past the last step: the reference returns `last`
   *margin = fmin(c_at - target, target - c_before) / z;
   return found;

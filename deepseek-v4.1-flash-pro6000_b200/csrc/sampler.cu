@@ -4,6 +4,7 @@
 #include "stream_types.cuh"
 #include "flat.cuh"
 #include "replay.cuh"
+#include "phase_events.h"
 #include "host_error.h"
 #include <cmath>
 #include <cstdlib>
@@ -83,6 +84,39 @@ double bound_scale() {
 }
 }  // namespace
 
+namespace ds41 {
+PhaseEvents &phase_events() {
+  static PhaseEvents p;
+  return p;
+}
+}  // namespace ds41
+
+extern "C" int ds41_b200_profile_phases(int enable) {
+  ds41::PhaseEvents &p = ds41::phase_events();
+  if (enable && !p.on) {
+    for (int i = 0; i < ds41::kPhaseMarks; ++i) {
+      const cudaError_t e = cudaEventCreate(&p.events[i]);
+      if (e != cudaSuccess) return int(e);
+    }
+    p.on = true;
+  } else if (!enable && p.on) {
+    p.on = false;
+    for (int i = 0; i < ds41::kPhaseMarks; ++i) cudaEventDestroy(p.events[i]);
+  }
+  p.next = 0;
+  return 0;
+}
+
+extern "C" int ds41_b200_profile_read(float *ms, int capacity) {
+  ds41::PhaseEvents &p = ds41::phase_events();
+  if (!p.on || p.next < 2 || !ms) return 0;
+  if (cudaEventSynchronize(p.events[p.next - 1]) != cudaSuccess) return -1;
+  int n = 0;
+  for (int i = 0; i + 1 < p.next && n < capacity; ++i, ++n)
+    if (cudaEventElapsedTime(&ms[n], p.events[i], p.events[i + 1]) != cudaSuccess) return -1;
+  return n;
+}
+
 extern "C" size_t ds41_b200_sample_scratch_bytes(int rows, int vocab) {
   if (rows < 1 || vocab < 1 || vocab > DS41_B200_MAX_VOCAB) return 0;
   return streaming_bytes(rows, vocab) + (flat_shape(rows, vocab) ? flat_scratch_bytes(rows) : 0) + replay_scratch_bytes();
@@ -151,12 +185,15 @@ extern "C" int ds41_b200_sample_logits(const ds41_b200_sample_args *p, cudaStrea
     a.pending = flat_pending(flat_scratch);
     e = launch_rows<kModeSample>(a, p->rows, stream);
     if (e != cudaSuccess) return int(e);
+    phase_mark(stream);
     // rows whose decision fell inside the rounding bound of the parallel sums: redone in the reference's own order
     ReplayArgs r{p->logits, p->logits_stride, p->vocab, p->rows, a.temperature, p->top_p, p->seeds, p->steps, p->slot,
                  p->purpose, p->tokens, status,
                  static_cast<unsigned char *>(flat_scratch) + flat_scratch_bytes(p->rows),
                  const_cast<int *>(flat_pending(flat_scratch)) + 1};
-    return int(launch_replay(r, stream));
+    e = launch_replay(r, stream);
+    phase_mark(stream);
+    return int(e);
   }
   if (streaming) {
     // streaming path: chunk records -> combine -> cluster kernel only for the rows the combine could not cover

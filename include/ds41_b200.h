@@ -327,6 +327,14 @@ int ds41_b200_score_logits(const ds41_b200_score_args *args, cudaStream_t stream
 int ds41_b200_logits_sha256(const float *logits, int rows, int vocab, int64_t logits_stride, uint8_t *digests,
                             cudaStream_t stream);
 
+/* Measurement hook (not thread-safe, off by default): with it on, the next ds41_b200_sample_logits call that takes the
+ * batch path records CUDA events on its stream between its kernels; ds41_b200_profile_read waits for the last one and
+ * returns the milliseconds of each interval, in launch order: statistics, histogram, window, masses, resolve, cluster
+ * kernel, replay (DS41_B200_PROFILE_PHASES of them; fewer when the call ended early; -1 on a CUDA error). */
+#define DS41_B200_PROFILE_PHASES 7
+int ds41_b200_profile_phases(int enable);
+int ds41_b200_profile_read(float *ms, int capacity);
+
 /* ---- test hook ---------------------------------------------------------------------------------------------------
  * out[i] = the samplers' own exp(x[i]) for x <= 0 (device pointers), so that its error can be measured against a
  * reference exponential.  No counterpart in the reference. */

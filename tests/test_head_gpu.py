@@ -56,7 +56,7 @@ def test_head_matches_oracle(pkg, oracle, M, N, K):
 
 @pytest.mark.parametrize("M", [1, 8, 64])
 def test_head_full_vocabulary(pkg, oracle, M):
-    """BASELINE config 2 shape: W e4m3 [129280,4096] ~ N(0,0.02^2) with fp32 scale per 128x128 block."""
+    """benchmark configuration 2 shape: W e4m3 [129280,4096] ~ N(0,0.02^2) with fp32 scale per 128x128 block."""
     N, K = 129280, 4096
     g = torch.Generator(device="cuda").manual_seed(7)
     w = torch.randn(N, K, device="cuda", generator=g) * 0.02

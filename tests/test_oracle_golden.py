@@ -78,7 +78,7 @@ def test_losslessness_statistics(oracle):
 
 
 def test_config1_fixture(oracle):
-    """Oracle reproduces the reference's tokens and MTP records on BASELINE config 1 (1,000 steps, two settings)."""
+    """Oracle reproduces the reference's tokens and MTP records on benchmark configuration 1 (1,000 steps, two settings)."""
     g = json.load(open(os.path.join(GOLD, "config1_reference.json")))
     V = g["vocab"]
     x = oracle.gen_logits(g["seed"], 1, V)[0]

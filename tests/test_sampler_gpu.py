@@ -47,7 +47,7 @@ def run(pkg, logits, t, top, seeds, steps, **kw):
 
 
 def test_config1_fixture(pkg, oracle):
-    """BASELINE config 1: the reference's tokens for 1,000 steps at (T=1, top-p=1) and (T=0.7, top-p=0.95)."""
+    """benchmark configuration 1: the reference's tokens for 1,000 steps at (T=1, top-p=1) and (T=0.7, top-p=0.95)."""
     g = json.load(open(os.path.join(GOLD, "config1_reference.json")))
     x = dev(oracle.gen_logits(g["seed"], 1, g["vocab"])).expand(g["steps"], g["vocab"])
     for runrec in g["runs"]:
@@ -97,7 +97,7 @@ def test_known_answers_from_core_cpp(pkg):
 
 @pytest.mark.parametrize("top_k,top", [(50, 0.9), (1, 1.0), (5, 1.0), (200, 0.5), (100000, 0.9)])
 def test_penalties_mask_topk(pkg, oracle, top_k, top):
-    """BASELINE config 4 at reduced batch: history penalties + allowed-token bitmask + top-k then top-p."""
+    """benchmark configuration 4 at reduced batch: history penalties + allowed-token bitmask + top-k then top-p."""
     rows, vocab = 16, 129280
     x = oracle.gen_logits(4, rows, vocab)
     hist = oracle.gen_history(4, rows, vocab, 4096)

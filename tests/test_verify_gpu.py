@@ -58,7 +58,7 @@ def same(got, want):
 @pytest.mark.parametrize("t,top,sigma", [(0.6, 0.95, 0.30), (1.0, 1.0, 0.5), (1.0, 0.9, 1.0), (0.0, 1.0, 0.5)])
 @pytest.mark.parametrize("drafts", [0, 2, 5])
 def test_config3_verification(pkg, oracle, t, top, sigma, drafts):
-    """BASELINE config 3 shape: sequences x (1 target + drafts) rows, V=129280."""
+    """benchmark configuration 3 shape: sequences x (1 target + drafts) rows, V=129280."""
     seqs, vocab = (32 if drafts == 2 else 8), 129280
     target = oracle.gen_logits(31, seqs * (drafts + 1), vocab)
     seeds, steps = np.arange(seqs) * 101 + 7, np.arange(seqs) + 1000
@@ -77,7 +77,7 @@ def test_config3_verification(pkg, oracle, t, top, sigma, drafts):
 
 
 def test_config1_mtp_fixture(pkg, oracle):
-    """The reference's own accept/resample records on BASELINE config 1 (first 150 steps of both settings)."""
+    """The reference's own accept/resample records on benchmark configuration 1 (first 150 steps of both settings)."""
     g = json.load(open(os.path.join(GOLD, "config1_reference.json")))
     V, n = g["vocab"], 150
     x = oracle.gen_logits(g["seed"], 1, V)[0]
