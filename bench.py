@@ -797,7 +797,27 @@ def main():
             line["cpu_baseline"] = cpu_baseline(name)
         print(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        # The captured step holds NCCL kernels: the graph goes first, then the communicator.  Tearing a communicator
+        # down can still block when a peer is already gone, so it gets a time limit; the result line is out by now.
+        sys.stdout.flush()
+        if hasattr(wl, "graph"):
+            wl.graph = None
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
+        closed = threading.Event()
+
+        def close():
+            try:
+                dist.destroy_process_group()
+            finally:
+                closed.set()
+
+        threading.Thread(target=close, daemon=True).start()
+        if not closed.wait(20.0):
+            sys.stderr.write(f"rank {rank}: destroy_process_group did not return within 20 s; leaving\n")
+            sys.stderr.flush()
+            os._exit(0)
 
 
 if __name__ == "__main__":

@@ -124,10 +124,13 @@ class StepGuard:
                     names = ", ".join(w for w, h in self.pending if not h.is_completed()) or "kernels"
                     self._fail("step did not finish", f"no completion within {self.timeout_s:g} s (pending: {names})")
         for what, work in self.pending:
-            exc = work.exception() if work.is_completed() else None
-            if exc is not None:
+            try:
+                failed = work.is_completed() and not work.is_success()
+            except Exception:   # the handle cannot be queried on this build: the event wait above is the check
+                failed = False
+            if failed:
                 self.pending = []
-                self._fail(what, exc)
+                self._fail(what, "the process group recorded an error for this collective")
         self.pending = []
 
     def abort(self):
