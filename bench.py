@@ -39,10 +39,14 @@ DRAFT_SIGMA = 0.30
 # their traffic grows in proportion to the rows of a launch and is stored per row; the head's is stored per launch of
 # the named workload.
 NCU_TRAFFIC_PER_ROW = {
-    # profiles/sampler_batch_kernels_256rows.md (256 rows x 129280 fp32 = 132.4 MB algorithmic per pass)
-    "flat_stats_kernel": None, "flat_hist_kernel": None, "flat_window_kernel": None, "flat_mass_kernel": None,
-    "flat_resolve_kernel": None, "row_kernel": None, "replay_sample_kernel": None,
+    # profiles/sampler_batch_kernels_256rows.md: one launch of each kernel at 256 rows x 129280 fp32 (132.38 MB per
+    # pass over the logits), read + written
+    "flat_hist_kernel": 137.8e6 / 256, "flat_window_kernel": 4.23e6 / 256, "flat_mass_kernel": 132.76e6 / 256,
+    "flat_resolve_kernel": 2.40e6 / 256, "row_kernel": 0.07e6 / 256, "replay_sample_kernel": 0.07e6 / 256,
+    # not launched in that capture (the head's epilogue had left the row records): one read of the logits, extrapolated
+    "flat_stats_kernel": 132.38e6 / 256,
 }
+EXTRAPOLATED_TRAFFIC = ("flat_stats_kernel",)
 NCU_TRAFFIC_PER_LAUNCH = {
     # head_fp8_kernel<64,128>, 64 x 129280 x 4096: 530.38 MB read + 28.19 MB written (profiles/head_fp8_kernel_b64_full_vocab.md)
     ("cfg2_b64", "head_fp8_kernel"): 558.6e6,
@@ -767,7 +771,9 @@ def main():
                                      for k, v in phases.items()}
                 entry_["dominant_kernel"] = top
                 entry_["traffic"] = sampler_traffic(phases, rows_here)
-                entry_["traffic_note"] = "per-kernel ncu captures at 256 rows, scaled by rows (streaming kernels)"
+                entry_["traffic_note"] = ("per-kernel ncu captures at 256 rows, scaled by rows (streaming kernels)" +
+                                          ("; flat_stats_kernel extrapolated as one read of the logits"
+                                           if phases.get("flat_stats_kernel", 0) > 0.004 else ""))
             per_kernel.append(entry_)
         per_kernel.sort(key=lambda k: -k["kernel_ms"])
         roof = dict(per_kernel[0])

@@ -769,8 +769,11 @@ cudaError_t launch_flat(FlatArgs a, void *scratch, cudaStream_t stream) {
   phase_mark(stream);
   flat_window_kernel<<<a.rows, kFT, 0, stream>>>(a);
   phase_mark(stream);
-  // the mass pass: eight warps per CTA, one 1024-id sub-region per warp and round
-  const int mass_parts = a.rows >= 64 ? 4 : 16;
+  // the mass pass: four warps per CTA, one 1024-id sub-region per warp and round.  Five CTAs fit an SM (740 at a time on
+  // the GPU), so the rows are cut into as many pieces as give about four waves or more: a grid of 1.4 waves (256 rows x
+  // 4 pieces) left a third of the SMs idle through its second wave
+  int mass_parts = 4;
+  while (mass_parts < 16 && a.rows * mass_parts < 2960) mass_parts <<= 1;
   FlatArgs m = a;
   m.parts = mass_parts;
   flat_mass_kernel<<<a.rows * mass_parts, kFlatMassThreads, 0, stream>>>(m);

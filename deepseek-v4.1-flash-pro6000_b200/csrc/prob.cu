@@ -247,9 +247,90 @@ __global__ void __launch_bounds__(kRT) verify_rows_kernel(VerifyRowsArgs<T> a) {
   }
 }
 
+// The transactions of ds41_b200_verify_logits whose status carries a certification bit, redone from the logits:
+// probability rows by the reference's rule (replay_probabilities), then verify_impl (sampling.cpp:39-53) on them, one
+// CTA per transaction, two rows in memory at a time.  A decision that is still within 16 * 2^-53 of its threshold keeps
+// its bit; everything else leaves with status 0.
+constexpr double kVerifyStillClose = 16.0 * kU;
+
+__global__ void __launch_bounds__(kRT) verify_replay_kernel(VerifyReplayArgs a) {
+  __shared__ ReplaySmem s;
+  extern __shared__ __align__(16) unsigned char dynamic[];
+  unsigned char *mine = a.scratch + size_t(blockIdx.x) * size_t(kReplayPad) * 28;
+  double *pbuf = reinterpret_cast<double *>(mine), *qbuf = pbuf + kReplayPad;
+  unsigned long long *key = reinterpret_cast<unsigned long long *>(mine + size_t(kReplayPad) * 16);
+  int *idx = reinterpret_cast<int *>(mine + size_t(kReplayPad) * 24);
+  ds41_spark_result *results = static_cast<ds41_spark_result *>(a.results);
+  const int n = a.vocab, count = a.drafts;
+  for (int first = 0; first < a.sequences; first += kRT) {
+    const int candidate = first + threadIdx.x;
+    if (!__syncthreads_or(candidate < a.sequences && a.status[candidate] > 0)) continue;
+    for (int seq = first + blockIdx.x; seq < min(a.sequences, first + kRT); seq += gridDim.x) {
+      if (!(a.status[seq] > 0)) continue;   // the same in every thread
+      const uint64_t seed = a.seeds[seq], step = a.steps[seq];
+      ds41_spark_result r{};
+      int status = 0, close = 0;
+      for (int k = 0; k < count && status == 0 && !r.rejected; ++k) {
+        const int d = a.ids[size_t(seq) * count + k];   // in range: the first pass rejects the transaction otherwise
+        const Replayed rp = replay_probabilities(s, a.target + (size_t(seq) * (count + 1) + k) * n, n, a.t, a.top_p, pbuf,
+                                                 key, idx, dynamic);
+        const Replayed rq = replay_probabilities(s, a.draft + (size_t(seq) * count + k) * n, n, a.t, a.top_p, qbuf, key,
+                                                 idx, dynamic);
+        if (rp.cut_margin < kVerifyStillClose || rq.cut_margin < kVerifyStillClose) close |= 2;
+        const double pd = pbuf[d], qd = qbuf[d];
+        if (!(qd > 0)) { status = DS41_B200_ROW_DRAFT; break; }
+        const double u = philox_uniform(seed, step, uint32_t(k), 2u);
+        const double ratio = pd / qd;
+        const bool accept = u < fmin(1.0, ratio);
+        if (ratio < 1.0 && fabs(u - ratio) < kVerifyStillClose * ratio) close |= 4;
+        if (accept) {
+          r.tokens[r.emitted++] = d;
+          ++r.accepted_drafts;
+        } else {
+          double margin;
+          const int token = replay_draw(s, n, philox_uniform(seed, step, uint32_t(k), 3u),
+                                        [pbuf, qbuf](int i) { return fmax(0.0, pbuf[i] - qbuf[i]); }, &margin);
+          if (token < 0) { status = DS41_B200_ROW_EMPTY; break; }
+          if (margin < kVerifyStillClose) close |= 8;
+          r.tokens[r.emitted++] = token;
+          r.rejected = 1;
+        }
+      }
+      if (status == 0 && !r.rejected) {
+        const Replayed rp = replay_probabilities(s, a.target + (size_t(seq) * (count + 1) + count) * n, n, a.t, a.top_p,
+                                                 pbuf, key, idx, dynamic);
+        if (rp.cut_margin < kVerifyStillClose) close |= 2;
+        double margin;
+        const int token = replay_draw(s, n, philox_uniform(seed, step, uint32_t(count), 0u),
+                                      [pbuf](int i) { return pbuf[i]; }, &margin);
+        if (margin < kVerifyStillClose) close |= 1;
+        r.tokens[r.emitted++] = token;
+      }
+      if (threadIdx.x == 0) {
+        if (status) { r = ds41_spark_result{}; r.emitted = -1; }
+        else r.accepted_input_rows = r.accepted_drafts + 1;
+        results[seq] = r;
+        a.status[seq] = status ? status : close;
+      }
+      __syncthreads();
+    }
+  }
+}
+
 int grid_for(int items) { return items < 592 ? items : 592; }
 
 }  // namespace
+}  // namespace ds41
+
+namespace ds41 {
+cudaError_t launch_verify_replay(const VerifyReplayArgs &a, cudaStream_t stream) {
+  const cudaError_t e = cudaFuncSetAttribute(verify_replay_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             int(kReplayDynamicBytes));
+  if (e != cudaSuccess) return e;
+  const int ctas = a.sequences < kVerifyReplayCtas ? a.sequences : kVerifyReplayCtas;
+  verify_replay_kernel<<<ctas, kRT, kReplayDynamicBytes, stream>>>(a);
+  return cudaGetLastError();
+}
 }  // namespace ds41
 
 using namespace ds41;

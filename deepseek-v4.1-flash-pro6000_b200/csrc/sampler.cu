@@ -72,8 +72,11 @@ int flat_min_rows() {
   return value;
 }
 bool flat_shape(int rows, int vocab) { return rows >= flat_min_rows() && vocab >= kFlatMinVocab; }
-// DS41_BOUND_SCALE (read once; tests only) multiplies the batch path's certification bounds, so that many rows are
-// flagged as uncertified and take the exact replay
+}  // namespace
+
+namespace ds41 {
+// DS41_BOUND_SCALE (read once; tests only) multiplies the certification bounds of the batch path and of the
+// verification kernel, so that many decisions are flagged as uncertified and take the exact replay
 double bound_scale() {
   static const double value = [] {
     const char *e = getenv("DS41_BOUND_SCALE");
@@ -82,9 +85,6 @@ double bound_scale() {
   }();
   return value;
 }
-}  // namespace
-
-namespace ds41 {
 PhaseEvents &phase_events() {
   static PhaseEvents p;
   return p;

@@ -9,8 +9,10 @@
 //   2. one cluster per sequence walks the positions: accept test from the two rows' statistics and the two logits at
 //      the draft id; on the first rejection the residual max(0,p-q) is drawn by an inverse CDF streamed from the two
 //      rows (normally still L2 resident), otherwise the bonus token is drawn from the last target row.
+#include <atomic>
 #include "ds41_b200.h"
 #include "host_error.h"
+#include "replay.cuh"
 #include "row_kernel.cuh"
 #include "stream_types.cuh"
 #include <cmath>
@@ -33,6 +35,7 @@ struct VerifyArgs {
   const uint64_t *seeds, *steps;
   ds41_spark_result *results;
   int32_t *status;
+  double bound_scale;   // 1 (tests widen the bounds to exercise the replay)
 };
 
 struct Measure {  // one row's probability measure: P(id) = survives ? exp((x-max)/T) / e_kept : 0
@@ -85,7 +88,7 @@ __global__ void __launch_bounds__(kThreads, 2) verify_kernel(VerifyArgs a) {
       const double ratio = fmin(1.0, pd / qd);
       const double u = philox_uniform(seed, step, uint32_t(k), 2);
       accept = u < ratio;
-      if (ratio < 1.0 && fabs(u - ratio) <= (P.bound() + Q.bound() + 16 * kU) * ratio) status |= 4;
+      if (ratio < 1.0 && fabs(u - ratio) <= (P.bound() + Q.bound() + 16 * kU) * a.bound_scale * ratio) status |= 4;
       if (!accept) {
         // residual draw: inverse CDF over max(0, P - Q) in id order
         auto value = [&](int j) { const int id = c.begin + j; return fmax(0.0, P.at(id) - Q.at(id)); };
@@ -93,8 +96,9 @@ __global__ void __launch_bounds__(kThreads, 2) verify_kernel(VerifyArgs a) {
         int amb = 0;
         double total = 0;
         const int support = min(a.vocab, P.st.kept + Q.st.kept);
-        const int token = draw_token(c, philox_uniform(seed, step, uint32_t(k), 3), (2.0 * support + 256.0) * kU,
-                                     P.bound() + Q.bound(), value, &amb, &total);
+        const int token = draw_token(c, philox_uniform(seed, step, uint32_t(k), 3),
+                                     (2.0 * support + 256.0) * kU * a.bound_scale, (P.bound() + Q.bound()) * a.bound_scale,
+                                     value, &amb, &total);
         if (!(total > 0) || token < 0) { status = -2; break; }
         if (amb) status |= 8;
         r.tokens[r.emitted++] = token;
@@ -113,8 +117,8 @@ __global__ void __launch_bounds__(kThreads, 2) verify_kernel(VerifyArgs a) {
       region_sums(c, value);
       int amb = 0;
       double total = 0;
-      const int token = draw_token(c, philox_uniform(seed, step, uint32_t(D), 0), (2.0 * P.st.kept + 256.0) * kU, 0.0,
-                                   value, &amb, &total);
+      const int token = draw_token(c, philox_uniform(seed, step, uint32_t(D), 0),
+                                   (2.0 * P.st.kept + 256.0) * kU * a.bound_scale, 0.0, value, &amb, &total);
       if (amb) status |= 1;
       r.tokens[r.emitted++] = token;
     }
@@ -130,12 +134,21 @@ __global__ void __launch_bounds__(kThreads, 2) verify_kernel(VerifyArgs a) {
 
 }  // namespace ds41
 
+namespace ds41 {
+namespace {
+// [row statistics][chunk records of the streaming path], rounded up to 16 bytes; the replay's rows follow
+size_t verify_streaming_bytes(int sequences, int drafts, int vocab) {
+  const size_t rows = size_t(sequences) * size_t(2 * drafts + 1);
+  return (rows * sizeof(RowStats) + rows * chunks_for(vocab) * sizeof(ChunkRecord) + 15) & ~size_t(15);
+}
+}  // namespace
+}  // namespace ds41
+
 using namespace ds41;
 
 extern "C" size_t ds41_b200_verify_scratch_bytes_for(int sequences, int drafts, int vocab) {
   if (sequences < 1 || drafts < 0 || drafts > 5 || vocab < 1 || vocab > DS41_B200_MAX_VOCAB) return 0;
-  const size_t rows = size_t(sequences) * size_t(2 * drafts + 1);
-  return rows * sizeof(RowStats) + rows * chunks_for(vocab) * sizeof(ChunkRecord);
+  return verify_streaming_bytes(sequences, drafts, vocab) + verify_replay_scratch_bytes();
 }
 extern "C" size_t ds41_b200_verify_scratch_bytes(int sequences, int drafts) {
   return ds41_b200_verify_scratch_bytes_for(sequences, drafts, DS41_B200_MAX_VOCAB);
@@ -158,7 +171,8 @@ extern "C" int ds41_b200_verify_logits(const ds41_b200_verify_args *p, cudaStrea
   RowStats *qstats = pstats + size_t(p->sequences) * (p->drafts + 1);
   // with room for the chunk records the row statistics come from the streaming path (cluster kernel only for rows
   // it cannot cover); with statistics-only scratch every row goes through the cluster kernel
-  const bool streaming = p->scratch_bytes >= ds41_b200_verify_scratch_bytes_for(p->sequences, p->drafts, p->vocab);
+  const size_t streaming_need = verify_streaming_bytes(p->sequences, p->drafts, p->vocab);
+  const bool streaming = p->scratch_bytes >= streaming_need;
   ChunkRecord *records = reinterpret_cast<ChunkRecord *>(pstats + stat_rows);
   RowArgs a{};
   a.vocab = p->vocab; a.logits_stride = p->vocab;
@@ -195,7 +209,7 @@ extern "C" int ds41_b200_verify_logits(const ds41_b200_verify_args *p, cudaStrea
     configured_device = dev;
   }
   VerifyArgs v{p->target_logits, p->draft_logits, p->draft_ids, pstats, qstats, p->drafts, p->vocab, a.temperature,
-               p->seeds, p->steps, p->results, p->status};
+               p->seeds, p->steps, p->results, p->status, bound_scale()};
   const int cl = cluster_size_for(p->vocab);
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(unsigned(p->sequences) * cl);
@@ -206,7 +220,17 @@ extern "C" int ds41_b200_verify_logits(const ds41_b200_verify_args *p, cudaStrea
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = cl; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr; cfg.numAttrs = 1;
-  return int(cudaLaunchKernelEx(&cfg, verify_kernel, v));
+  e = cudaLaunchKernelEx(&cfg, verify_kernel, v);
+  if (e != cudaSuccess) return int(e);
+  // transactions with a certification bit set: redone in the reference's order of operations, when the caller gave
+  // the status words and room for two probability rows per CTA (the scratch-free entry point has neither)
+  if (!greedy && p->status && p->scratch_bytes >= streaming_need + verify_replay_scratch_bytes()) {
+    VerifyReplayArgs r{p->target_logits, p->draft_logits, p->draft_ids, p->sequences, p->drafts, p->vocab, a.temperature,
+                       p->top_p, p->seeds, p->steps, p->results, p->status,
+                       static_cast<unsigned char *>(p->scratch) + streaming_need};
+    e = launch_verify_replay(r, stream);
+  }
+  return int(e);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -234,7 +258,7 @@ namespace {
 constexpr int kStaticStatRows = 1024;  // sequences * (2*drafts + 1) may not exceed this
 static __device__ __align__(256) unsigned char g_static_stats[kStaticStatRows * sizeof(RowStats)];
 constexpr int kMaxDevices = 64;
-void *g_static_stats_addr[kMaxDevices] = {};
+std::atomic<void *> g_static_stats_addr[kMaxDevices];   // zero-initialised (static storage)
 }  // namespace
 }  // namespace ds41
 
@@ -252,13 +276,13 @@ extern "C" int ds41_b200_verify_logits_static(const ds41_b200_verify_args *p, cu
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return int(e);
   if (dev < 0 || dev >= kMaxDevices) return invalid("device ordinal beyond the static scratch table");
-  void *addr = g_static_stats_addr[dev];
+  void *addr = g_static_stats_addr[dev].load(std::memory_order_relaxed);
   if (!addr) {  // first call on this device: resolve the device address of the array (idempotent, so a race between
                 // two first calls only repeats the lookup)
     e = cudaGetSymbolAddress(&addr, g_static_stats);
     if (e != cudaSuccess) return int(e);
     if (!addr) return invalid("cudaGetSymbolAddress returned a null address");
-    g_static_stats_addr[dev] = addr;
+    g_static_stats_addr[dev].store(addr, std::memory_order_relaxed);
   }
   ds41_b200_verify_args with_scratch = *p;
   with_scratch.scratch = addr;

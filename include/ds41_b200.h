@@ -191,6 +191,8 @@ int ds41_b200_verify_logits(const ds41_b200_verify_args *args, cudaStream_t stre
  * the reference.  args->scratch and args->scratch_bytes are ignored: the per-row statistics live in a 48 KiB device
  * array built into the library, so sequences*(2*drafts+1) may not exceed
  * ds41_b200_verify_logits_static_max_rows() (1024); larger requests return cudaErrorInvalidValue with a message.
+ * Small calls (up to five full-vocabulary rows, e.g. one sequence with two drafts) take the chunk + combine path and
+ * keep their 544-byte chunk records in the same array, behind the statistics.
  * The first call on each device looks up the array's address (make it before any stream capture); no call
  * allocates.  All calls share the array, so calls that could overlap on the GPU must be serialised by the caller. */
 int ds41_b200_verify_logits_static_max_rows(void);

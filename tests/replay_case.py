@@ -15,7 +15,39 @@ import __graft_entry__ as entry  # noqa: E402
 import oracle_lib  # noqa: E402
 
 
+def verify_case(seqs, vocab, t, top):
+    """Speculative verification with widened bounds: flagged transactions come back from the replay with the oracle's
+    records; prints how many transactions were flagged without the replay (status words of a scratch-limited call)."""
+    pkg = entry.load_package()
+    orc = oracle_lib.Oracle()
+    drafts = 2
+    target = orc.gen_logits(51, seqs * (drafts + 1), vocab)
+    base = target.reshape(seqs, drafts + 1, vocab)[:, :drafts].reshape(-1, vocab)
+    draft = orc.gen_perturbed(51, base, 0.4)
+    seeds, steps = np.arange(seqs, dtype=np.uint64) + 3, np.arange(seqs, dtype=np.uint64) * 7 + 2
+    ids = np.zeros((seqs, drafts), np.int32)
+    for k in range(drafts):
+        ids[:, k], _ = orc.sample_rows(draft[k::drafts], t, top, seeds, steps, slot=k, purpose=1, threads=8)
+    want, wst = orc.verify_rows(target, draft, ids.reshape(-1), drafts, t, top, seeds, steps, threads=8)
+    dev = torch.device("cuda", 0)
+    cu = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    args = (cu(target), cu(draft), cu(ids.reshape(-1)), drafts, t, top, cu(seeds.view(np.int64)), cu(steps.view(np.int64)))
+    res, st = pkg.verify_logits(*args)
+    # the same call with room for the statistics and chunk records only: no replay, the bits stay
+    full = pkg.verify_scratch_bytes(seqs, drafts, vocab)
+    small = torch.zeros(full - 2 * 131072 * 28, dtype=torch.uint8, device=dev)
+    res0, st0 = pkg.verify_logits(*args, scratch=small)
+    torch.cuda.synchronize()
+    got = pkg.results_to_numpy(res)
+    same = all((got[f] == want[f]).all() for f in ("tokens", "emitted", "accepted_drafts", "rejected"))
+    print(json.dumps({"records_equal": bool(same), "status": np.unique(st.cpu().numpy()).tolist(),
+                      "flagged_without_replay": int((st0.cpu().numpy() > 0).sum()),
+                      "oracle_status": np.unique(wst).tolist(), "sequences": seqs}))
+
+
 def main():
+    if sys.argv[1] == "verify":
+        return verify_case(int(sys.argv[2]), int(sys.argv[3]), float(sys.argv[4]), float(sys.argv[5]))
     rows, vocab = int(sys.argv[1]), int(sys.argv[2])
     t, top = float(sys.argv[3]), float(sys.argv[4])
     pkg = entry.load_package()

@@ -41,3 +41,21 @@ def test_real_bounds_flag_only_the_exact_tie():
 def test_smaller_vocabulary():
     r = run_case(3e6, 24, 50000, 0.7, 0.9)
     assert r["replayed"] >= 6 and r["tokens_equal"] and r["status"] == [0], r
+
+
+def run_verify_case(scale, seqs, vocab, t, top):
+    env = dict(os.environ, DS41_BOUND_SCALE=str(scale))
+    out = subprocess.run([sys.executable, os.path.join(HERE, "replay_case.py"), "verify", str(seqs), str(vocab), str(t),
+                          str(top)], env=env, capture_output=True, text=True, timeout=900)
+    assert out.returncode == 0, out.stderr[-2000:]
+    return json.loads(out.stdout.strip().splitlines()[-1])
+
+
+@pytest.mark.parametrize("t,top", [(0.6, 0.95), (1.0, 1.0)])
+def test_flagged_transactions_are_replayed_exactly(t, top):
+    """Speculative verification: with widened bounds the accept tests and the residual / bonus draws are flagged
+    (bits 4, 8, 1); the replay redoes those transactions from the logits in the reference's order
+    (sampling.cpp:39-53) and they leave with the oracle's records and status 0."""
+    r = run_verify_case(1e12, 24, 129280, t, top)
+    assert r["flagged_without_replay"] >= 6, r
+    assert r["records_equal"] and r["status"] == [0], r

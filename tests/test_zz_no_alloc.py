@@ -67,6 +67,36 @@ def test_static_scratch_matches_caller_scratch_twice(pkg, oracle):
         assert (emitted >= 1).all() and (emitted <= drafts + 1).all()
 
 
+@pytest.mark.parametrize("seqs,drafts,vocab,t,top", [
+    (1, 2, 129280, 0.6, 0.95),    # the common decode step: five rows, the chunk + combine path inside the static array
+    (1, 1, 129280, 1.0, 1.0),
+    (3, 0, 129280, 0.8, 0.9),     # no drafts: the bonus sample only
+    (4, 2, 129280, 0.0, 1.0),     # greedy
+    (1, 5, 50000, 0.7, 0.9),
+])
+def test_static_scratch_small_calls(pkg, oracle, seqs, drafts, vocab, t, top):
+    """Calls small enough for the streaming path keep their chunk records in the built-in array too; the results are
+    those of the call with caller scratch, and a larger call right after still works (no record outlives its call)."""
+    t_draw = t if t > 0 else 1.0
+    target, draft, ids, seeds, steps = make_inputs(oracle, 70 + seqs + drafts, seqs, max(drafts, 1), vocab, t_draw, top)
+    if drafts == 0:
+        target = target[::2].contiguous()          # one target row per sequence
+        draft, ids = draft[:0], ids[:0]
+        draft = torch.zeros((1, vocab), device="cuda")   # never read: drafts == 0
+        ids = torch.zeros(1, dtype=torch.int32, device="cuda")
+    want_res, want_st = pkg.verify_logits(target, draft, ids, drafts, t, top, seeds, steps)
+    rc, got_res, got_st = call_static(pkg, target, draft, ids, drafts, t, top, seeds, steps)
+    torch.cuda.synchronize()
+    assert rc == 0, pkg.last_error()
+    assert torch.equal(got_st, want_st) and (got_st >= 0).all(), (got_st, want_st)
+    assert torch.equal(got_res, want_res)
+    big = make_inputs(oracle, 91, 16, 2, 32768, 0.9, 0.9)
+    want_res, want_st = pkg.verify_logits(big[0], big[1], big[2], 2, 0.9, 0.9, big[3], big[4])
+    rc, got_res, got_st = call_static(pkg, big[0], big[1], big[2], 2, 0.9, 0.9, big[3], big[4])
+    torch.cuda.synchronize()
+    assert rc == 0 and torch.equal(got_res, want_res) and torch.equal(got_st, want_st)
+
+
 def test_static_scratch_rejects_oversized_requests(pkg):
     assert pkg.lib().ds41_b200_verify_logits_static_max_rows() == 1024
     a = pkg.VerifyArgs()
