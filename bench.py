@@ -59,11 +59,11 @@ def sampler_traffic(phases, rows):
     """Bytes one sampler call moves, from the per-kernel capture table: the kernels that ran (phases) x rows."""
     total = 0.0
     for k in phases:
-        per_row = NCU_TRAFFIC_PER_ROW.get(k)
-        if per_row is None:
-            if phases[k] > 0.004:   # a kernel that did work and has no capture: the call's traffic is unknown
-                return None
+        if phases[k] <= 0.004:      # not launched in this call (the interval is the gap between two event records)
             continue
+        per_row = NCU_TRAFFIC_PER_ROW.get(k)
+        if per_row is None:         # a kernel that did work and has no capture: the call's traffic is unknown
+            return None
         total += per_row * rows
     return total
 
@@ -366,7 +366,8 @@ class VerifyWorkload:
         for k in range(3):  # three input sets (3 x 83 MB > L2) cycled between steps
             target = zipf_gauss_logits(torch, device, seqs * (drafts + 1), 100 + k)
             base = target.view(seqs, drafts + 1, VOCAB)[:, :drafts].reshape(-1, VOCAB)
-            draft = base + sigma * torch.randn(base.shape, device=device)
+            draft = base + sigma * torch.randn(base.shape, device=device,
+                                               generator=torch.Generator(device=device).manual_seed(200 + k))
             seeds = torch.arange(seqs, dtype=torch.int64, device=device) + 5
             steps = torch.full((seqs,), 1000 + k, dtype=torch.int64, device=device)
             ids = torch.empty(seqs * drafts, dtype=torch.int32, device=device)

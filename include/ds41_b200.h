@@ -346,6 +346,10 @@ int ds41_b200_test_exp_nonpos(const double *x, double *out, int n, cudaStream_t 
  * bound against a reference exponential. */
 int ds41_b200_test_batch_weight(const float *y, float max_logit, double temperature, double *out, int n,
                                 cudaStream_t stream);
+/* out = {index or -1, acc, acc before that term} of the chain acc += v[i] over n doubles with every rounding of the
+ * one-thread loop (the replay's parallel form of the reference's sums).  mode 0: the sum; 1: stop when !(acc <
+ * threshold); 2: stop when threshold < acc. */
+int ds41_b200_test_sequential(const double *v, int n, int mode, double threshold, double *out, cudaStream_t stream);
 
 #ifdef __cplusplus
 }
