@@ -212,8 +212,9 @@ class HeadSample:
                                                                               VOCAB, temperature, top_p, strategy)
             strategy = self.sharded.strategy  # "candidates" if the peer buffers could not be mapped
             self.exchange_note = self.sharded.exchange_error
-            # rows: quantise, head (+ peer stores), flat_stats / hist / window / mass / resolve, cluster kernel, replay
-            self.launches_per_step = 9 if strategy == "rows" else 6
+            # rows: quantise, head (+ peer stores and the row records merged into the owners), flat_hist / window / mass /
+            # resolve, cluster kernel, replay
+            self.launches_per_step = 8 if strategy == "rows" else 6
             if strategy == "rows":
                 self.sampler_rows = self.sharded.exchange.my_rows
 
@@ -227,9 +228,9 @@ class HeadSample:
 
     def sampler_call(self):
         """The step's sampler call alone, on the logits the last step left (for the per-kernel phase events)."""
-        if self.sharded:
-            if self.sharded.mode() == "rows" and self.sampler_rows:
-                self.sharded.exchange.sample_mine(self.t, self.top_p, self.seeds, self.steps)
+        if self.sharded:   # a whole eager step: the owners' row records are cleared once read, so the sampler call
+            if self.sharded.mode() == "rows":   # cannot be repeated alone (the phase events only see its kernels)
+                self.step(0, self.hidden, captured=True)
             return
         self.pkg.sample_logits(self.logits, self.t, self.top_p, self.seeds, self.steps, tokens=self.tokens,
                                status=self.status, scratch=self.scratch, row_extremes=self.extremes)
@@ -304,17 +305,34 @@ class HeadSample:
         tokens of step i before it returns."""
         torch = self.torch
         main = torch.cuda.current_stream()
+        # Several GPUs: the step's hidden states cross PCIe once for the whole job: every rank copies its 1/N of the
+        # rows from the host and the ranks all-gather them over NVLink (every rank's head slice needs every row).  Both
+        # happen on the side stream, one step ahead, with a communicator of their own (collectives of one communicator
+        # must not run on two streams at once).
+        split = bool(self.sharded) and self.B % self.world == 0
         if not hasattr(self, "copy_stream"):
             self.copy_stream = torch.cuda.Stream(device=self.device)
-            self.staging = [torch.empty_like(self.hidden), torch.empty_like(self.hidden)]
+            rows = self.B // self.world if split else self.B
+            self.my_rows0 = self.rank * rows if split else 0
+            self.slices = [torch.empty_like(self.hidden[:rows]), torch.empty_like(self.hidden[:rows])]
+            self.staging = [torch.empty_like(self.hidden), torch.empty_like(self.hidden)] if split else self.slices
             self.staged = [torch.cuda.Event(), torch.cuda.Event()]
             self.consumed = [torch.cuda.Event(), torch.cuda.Event()]
             self.prefetched = None
+            if split:
+                import torch.distributed as dist
+                self.copy_group = dist.new_group()
         def prefetch(step):
             slot = step % 2
             with torch.cuda.stream(self.copy_stream):
                 self.copy_stream.wait_event(self.consumed[slot])  # the step that last used this buffer has read it
-                self.staging[slot].copy_(self.host_ring[step % len(self.host_ring)], non_blocking=True)
+                n = self.slices[slot].shape[0]
+                src = self.host_ring[step % len(self.host_ring)][self.my_rows0:self.my_rows0 + n]
+                self.slices[slot].copy_(src, non_blocking=True)
+                if split:
+                    import torch.distributed as dist
+                    dist.all_gather_into_tensor(self.staging[slot].view(-1), self.slices[slot].view(-1),
+                                                group=self.copy_group)
                 self.staged[slot].record(self.copy_stream)
             self.prefetched = step
         if self.prefetched != i:
@@ -324,9 +342,9 @@ class HeadSample:
         main.wait_event(self.staged[slot])
         self.hidden.copy_(self.staging[slot], non_blocking=True)
         self.consumed[slot].record(main)
-        prefetch(i + 1)
         self.graph_step(i, from_host=True)
         self.tokens_host.copy_(self.tokens, non_blocking=True)
+        prefetch(i + 1)   # enqueued while the device runs this step
         if self.sharded:
             self.sharded.guard.finish()   # the same wait, with the guard's time limit and its error reporting
         else:

@@ -168,6 +168,9 @@ struct HeadArgs {
   // maximum, the minimum and a finiteness flag of the logits it produces for its batch row and merges them with atomic
   // maxima when it leaves the row, so the sampler's own pass over the logits for these three numbers can be skipped.
   HeadRowStats *row_stats;
+  // The same records in the row-scattered variant: row m's record lies owner_stats_offset bytes behind owner_base[owner]
+  // at index m % rows_per_owner (0: none).  Several GPUs merge into one record, so those atomics have system scope.
+  long long owner_stats_offset;
   int stages;            // shared-memory stages of the TMA ring (host: HeadSmem::stages)
   int group;             // K blocks per stage: every row of a weight tile is fetched as group*128 contiguous bytes
 };
@@ -275,17 +278,29 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     // ascending order, so a strict comparison keeps the first maximum)
     float st_best = -CUDART_INF_F, st_low = CUDART_INF_F, st_bad = 0.f;
     int st_id = 0x7fffffff;
+    const bool stats_on = p.row_stats != nullptr || p.owner_stats_offset != 0;
     auto flush_stats = [&](int bt_of) {
       const int m = bt_of * kRows + row;
-      if (p.row_stats && st_id != 0x7fffffff && row < kRows && m < p.M) {
+      if (stats_on && st_id != 0x7fffffff && row < kRows && m < p.M) {
         auto ordered = [](float v) {
           const uint32_t bits = __float_as_uint(v == 0.f ? 0.f : v);  // -0 and +0 are the same logit
           return bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u);
         };
-        HeadRowStats *rs = p.row_stats + m;
-        atomicMax(&rs->max_key, (unsigned long long)(ordered(st_best)) << 32 | (0xffffffffu - uint32_t(st_id)));
-        atomicMax(&rs->min_key, ~ordered(st_low));
-        if (st_bad != st_bad) atomicOr(&rs->flags, 1u);
+        const unsigned long long key = (unsigned long long)(ordered(st_best)) << 32 |
+                                       (0xffffffffu - uint32_t(st_id + p.col_offset));
+        if (p.owner_stats_offset) {
+          const int owner = m / p.rows_per_owner;
+          HeadRowStats *rs = reinterpret_cast<HeadRowStats *>(reinterpret_cast<unsigned char *>(p.owner_base[owner]) +
+                                                              p.owner_stats_offset) + (m - owner * p.rows_per_owner);
+          atomicMax_system(&rs->max_key, key);
+          atomicMax_system(&rs->min_key, ~ordered(st_low));
+          if (st_bad != st_bad) atomicOr_system(&rs->flags, 1u);
+        } else {
+          HeadRowStats *rs = p.row_stats + m;
+          atomicMax(&rs->max_key, key);
+          atomicMax(&rs->min_key, ~ordered(st_low));
+          if (st_bad != st_bad) atomicOr(&rs->flags, 1u);
+        }
       }
       st_best = -CUDART_INF_F; st_low = CUDART_INF_F; st_bad = 0.f; st_id = 0x7fffffff;
     };
@@ -347,7 +362,7 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       // 32 rows with 16 bytes each; an 8 x 8 transpose of the 16-byte column groups across the lanes that share
       // l % 4 (butterflies at lane distances 4, 8, 16) turns that into 4 rows with 128 contiguous bytes each, which is
       // what a peer GPU's memory wants to be written with (and the local L2 as well).
-      if (alive && p.row_stats) {
+      if (alive && stats_on) {
         const int n0 = nt * kTileN + group * kMyCols;
         if (n0 + kMyCols <= p.N) {
 #pragma unroll
@@ -557,10 +572,28 @@ extern "C" int ds41_b200_head_fp8_stats(const void *a_e4m3, const float *a_scale
   return run_head(a_e4m3, a_scale, w_e4m3, w_scale, p, stream);
 }
 
+extern "C" int ds41_b200_head_fp8_scatter_stats(const void *a_e4m3, const float *a_scale, const void *w_e4m3,
+                                                const float *w_scale, float *const *owner_logits, int owners,
+                                                int rows_per_owner, int64_t logits_stride, int vocab_offset, int M,
+                                                int N, int K, int64_t stats_offset_bytes, int *error_flag,
+                                                cudaStream_t stream);
+
 extern "C" int ds41_b200_head_fp8_scatter(const void *a_e4m3, const float *a_scale, const void *w_e4m3,
                                           const float *w_scale, float *const *owner_logits, int owners,
                                           int rows_per_owner, int64_t logits_stride, int vocab_offset, int M, int N,
                                           int K, int *error_flag, cudaStream_t stream) {
+  return ds41_b200_head_fp8_scatter_stats(a_e4m3, a_scale, w_e4m3, w_scale, owner_logits, owners, rows_per_owner,
+                                          logits_stride, vocab_offset, M, N, K, 0, error_flag, stream);
+}
+
+extern "C" int ds41_b200_head_fp8_scatter_stats(const void *a_e4m3, const float *a_scale, const void *w_e4m3,
+                                                const float *w_scale, float *const *owner_logits, int owners,
+                                                int rows_per_owner, int64_t logits_stride, int vocab_offset, int M,
+                                                int N, int K, int64_t stats_offset_bytes, int *error_flag,
+                                                cudaStream_t stream) {
+  if (stats_offset_bytes < 0 || (stats_offset_bytes & 15) ||
+      (stats_offset_bytes && stats_offset_bytes < int64_t(rows_per_owner) * logits_stride * 4))
+    return invalid("scattered head: the row records must lie behind the owner's logits, 16-byte aligned");
   if (!a_e4m3 || !a_scale || !w_e4m3 || !w_scale || !owner_logits || M < 1 || N < 1 || K < 128 || K % 128 ||
       K > 16384 || owners < 1 || owners > kMaxOwners || rows_per_owner < 1 || vocab_offset < 0 ||
       logits_stride < int64_t(vocab_offset) + N || int64_t(owners) * rows_per_owner < M)
@@ -569,6 +602,7 @@ extern "C" int ds41_b200_head_fp8_scatter(const void *a_e4m3, const float *a_sca
   p.a_scale = a_scale; p.w_scale = w_scale; p.logits = nullptr; p.ldl = logits_stride;
   p.M = M; p.N = N; p.K = K; p.error_flag = error_flag;
   p.rows_per_owner = rows_per_owner; p.col_offset = vocab_offset;
+  p.owner_stats_offset = stats_offset_bytes;
   for (int r = 0; r < owners; ++r) {
     if (!owner_logits[r] && int64_t(r) * rows_per_owner < M) return invalid("scattered head: null owner buffer");
     p.owner_base[r] = owner_logits[r];

@@ -292,9 +292,9 @@ class RowExchange:
         lib.ds41_b200_peer_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
         lib.ds41_b200_peer_close.argtypes = [C.c_void_p]
         lib.ds41_b200_peer_free.argtypes = [C.c_void_p]
-        lib.ds41_b200_head_fp8_scatter.argtypes = [C.c_void_p] * 4 + [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int64,
-                                                                      C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
-                                                                      C.c_void_p]
+        lib.ds41_b200_head_fp8_scatter_stats.argtypes = [C.c_void_p] * 4 + [C.POINTER(C.c_void_p), C.c_int, C.c_int,
+                                                                            C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                                            C.c_int64, C.c_void_p, C.c_void_p]
         self._lib = lib
         # Every rank must end up with the same verdict (a rank that raised alone would leave the others waiting in the
         # next collective): failures are recorded, agreed on with one all-reduce, and only then raised everywhere.
@@ -302,7 +302,9 @@ class RowExchange:
         handle = C.create_string_buffer(64)
         mine = C.c_void_p()
         with torch.cuda.device(device):
-            rc = lib.ds41_b200_peer_alloc(self.rows_per_owner * vocab * 4, C.byref(mine), handle)
+            # [logits rows][16-byte row records the heads of all ranks merge their slice's extremes into]
+            self.stats_offset = self.rows_per_owner * vocab * 4
+            rc = lib.ds41_b200_peer_alloc(self.stats_offset + self.rows_per_owner * 16, C.byref(mine), handle)
         if rc:
             failure = f"ds41_b200_peer_alloc: cudaError {rc} ({pkg.last_error()})"
             mine = C.c_void_p()
@@ -341,6 +343,9 @@ class RowExchange:
         self.owner_ptrs = (C.c_void_p * self.world)(*ptrs)
         self.full = torch.as_tensor(_DeviceBlock(mine.value, (self.rows_per_owner, vocab), "<f4"), device=device)
         self.full.zero_()
+        self.stats = torch.as_tensor(_DeviceBlock(mine.value + self.stats_offset, (self.rows_per_owner, 16), "|u1"),
+                                     device=device)
+        self.stats.zero_()
         self.word = torch.zeros(1, dtype=torch.int32, device=device)
         self.packed = torch.full((2, self.rows_per_owner), -1, dtype=torch.int32, device=device)
         # scratch enables the sampler's batch path (grid-wide kernels over this rank's rows)
@@ -354,13 +359,13 @@ class RowExchange:
         """This rank's vocabulary slice of every row's logits, stored into the rows' owners."""
         M, K = a.shape
         with torch.cuda.device(self.device):
-            rc = self._lib.ds41_b200_head_fp8_scatter(a.data_ptr(), a_scale.data_ptr(), w.data_ptr(), w_scale.data_ptr(),
-                                                      self.owner_ptrs, self.world, self.rows_per_owner, self.vocab,
-                                                      vocab_offset, M, w.shape[0], K,
-                                                      error_flag.data_ptr() if error_flag is not None else None,
-                                                      C.c_void_p(torch.cuda.current_stream().cuda_stream))
+            rc = self._lib.ds41_b200_head_fp8_scatter_stats(
+                a.data_ptr(), a_scale.data_ptr(), w.data_ptr(), w_scale.data_ptr(), self.owner_ptrs, self.world,
+                self.rows_per_owner, self.vocab, vocab_offset, M, w.shape[0], K, self.stats_offset,
+                error_flag.data_ptr() if error_flag is not None else None,
+                C.c_void_p(torch.cuda.current_stream().cuda_stream))
         if rc:
-            raise RuntimeError(f"ds41_b200_head_fp8_scatter: cudaError {rc} ({self.pkg.last_error()})")
+            raise RuntimeError(f"ds41_b200_head_fp8_scatter_stats: cudaError {rc} ({self.pkg.last_error()})")
 
     def writers_done(self):
         """Stream-ordered: returns (on the stream) once every rank's head kernel has finished its peer stores."""
@@ -373,8 +378,12 @@ class RowExchange:
         kw.setdefault("scratch", self.scratch)
         if n:
             sl = slice(self.row0, self.row0 + n)
+            # the row records the heads of all ranks merged into this owner's buffer save the sampler its own pass for them
+            kw.setdefault("row_extremes", self.stats[:n])
             self.pkg.sample_logits(self.full[:n], temperature, top_p, seeds[sl], steps[sl], slot=slot, purpose=purpose,
                                    tokens=self.packed[0, :n], status=self.packed[1, :n], **kw)
+        # read: cleared for the next step's writers (ordered before them by the token all-gather that follows)
+        self.stats.zero_()
 
     def publish(self, tokens, status):
         """All-gather of every owner's (tokens, status); also orders the next step's writers after this step's readers."""

@@ -293,6 +293,15 @@ int ds41_b200_shard_combine(const ds41_b200_shard_combine_args *args, cudaStream
 int ds41_b200_head_fp8_scatter(const void *a_e4m3, const float *a_scale, const void *w_e4m3, const float *w_scale,
                                float *const *owner_logits, int owners, int rows_per_owner, int64_t logits_stride,
                                int vocab_offset, int M, int N, int K, int *error_flag, cudaStream_t stream);
+/* The same with per-row records for the sampler (see ds41_b200_head_fp8_stats): every owner's buffer holds, behind its
+ * logits at byte offset stats_offset_bytes (>= rows_per_owner * logits_stride * 4, a multiple of 16), rows_per_owner
+ * 16-byte records.  All ranks merge their slice's first maximum (with its global id), minimum and finiteness flag into
+ * the record of the row's owner with system-scope atomic maxima.  The OWNER zeroes its records after it has read them
+ * and before the collective that orders the next step's writers after this step's readers. */
+int ds41_b200_head_fp8_scatter_stats(const void *a_e4m3, const float *a_scale, const void *w_e4m3, const float *w_scale,
+                                     float *const *owner_logits, int owners, int rows_per_owner, int64_t logits_stride,
+                                     int vocab_offset, int M, int N, int K, int64_t stats_offset_bytes, int *error_flag,
+                                     cudaStream_t stream);
 /* Peer-visible device buffers (CUDA IPC; one process per GPU).  alloc: cudaMalloc + a 64-byte handle to hand to the
  * other ranks; open: map another rank's buffer (enables peer access to its device on first use); close / free undo
  * them.  Not stream ordered: set up once, outside the decode loop. */

@@ -105,13 +105,20 @@ def test_head_scatter_to_row_owners(pkg, oracle, M, owners):
     want = pkg.head_fp8(a, a_scale, wq, ws, error_flag=flag)
     per, plan = sharded.rows_plan(M, owners)
     assert sum(n for _, n in plan) == M
-    bufs = [torch.full((per, N), float("nan"), device="cuda") for _ in range(owners)]
+    # every owner's buffer: [per rows of logits][per 16-byte row records], as RowExchange lays it out
+    stats_offset = per * N * 4
+    raw = [torch.zeros(stats_offset + per * 16, dtype=torch.uint8, device="cuda") for _ in range(owners)]
+    bufs = [r[:stats_offset].view(torch.float32).view(per, N) for r in raw]
+    for b in bufs:
+        b.fill_(float("nan"))
     ex = sharded.RowExchange.__new__(sharded.RowExchange)  # buffers are local here: no IPC, only the launch wrapper
     ex.pkg, ex.device, ex.world, ex.rows_per_owner, ex.vocab = pkg, torch.device("cuda", 0), owners, per, N
+    ex.stats_offset = stats_offset
     import ctypes as C
     ex._lib = pkg.lib()
-    ex._lib.ds41_b200_head_fp8_scatter.argtypes = [C.c_void_p] * 4 + [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int64,
-                                                                     C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    ex._lib.ds41_b200_head_fp8_scatter_stats.argtypes = [C.c_void_p] * 4 + [C.POINTER(C.c_void_p), C.c_int, C.c_int,
+                                                                           C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                                           C.c_int64, C.c_void_p, C.c_void_p]
     ex.owner_ptrs = (C.c_void_p * owners)(*[b.data_ptr() for b in bufs])
     for v0, vn in sharded.shard_plan(N, owners):
         if vn:
@@ -120,6 +127,19 @@ def test_head_scatter_to_row_owners(pkg, oracle, M, owners):
     assert flag.item() == 0
     got = torch.cat([b[:n] for b, (_, n) in zip(bufs, plan)])
     assert torch.equal(got, want)
+    # the row records all "ranks" merged into the owners: first maximum with its global id, minimum, finite
+    rec = np.concatenate([r[stats_offset:].cpu().numpy().view(np.uint64).reshape(per, 2)[:n]
+                          for r, (_, n) in zip(raw, plan)])
+    w_np = want.cpu().numpy()
+    def unorder(o):
+        o = np.asarray(o, np.uint32)
+        return np.where(o >> 31, o ^ np.uint32(0x80000000), ~o).view(np.float32)
+    max_key = rec[:, 0]
+    assert (unorder(max_key >> np.uint64(32)) == w_np.max(axis=1)).all()
+    assert ((np.uint64(0xffffffff) - (max_key & np.uint64(0xffffffff))).astype(np.int64) == w_np.argmax(axis=1)).all()
+    low = (rec[:, 1] & np.uint64(0xffffffff)).astype(np.uint32)
+    assert (unorder(~low) == w_np.min(axis=1)).all()
+    assert ((rec[:, 1] >> np.uint64(32)) == 0).all()
 
 
 def test_peer_buffer_alloc_and_view(pkg):
