@@ -533,7 +533,13 @@ __global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
     mass_before = a.s.subsure[size_t(row) * kFlatSubs + tid];
     ksum[tid] = mass_before;
   }
-  z = flat_sum(red, z);
+  // the reference's chain for the normaliser rounds by at most 2^-53 times the SUM OF ITS PARTIAL SUMS (each addition
+  // errs by half an ulp of its own result); that sum is at most 1024 * (normaliser through sub-region j) over the
+  // sub-regions j: about half of vocab * z on a row without structure, instead of the worst case vocab * z
+  double z_total;
+  const double z_through = flat_exclusive(red, z, &z_total) + z;
+  const double chain_terms = double(kFlatSub) * flat_sum(red, tid < kFlatSubs ? z_through : 0.0) / z_total * (1.0 + 1e-9);
+  z = z_total;
   mass_before = flat_sum(red, mass_before);
   bool ok = listed <= kFlatList && (full || listed >= 1) && (a.s.lcount[row * 4 + 1] & 2) == 0;
   const int n = ok ? listed : 0;
@@ -595,9 +601,10 @@ __global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
     }
     const double through0 = mass_before + flat_prefix2(red, e[0], e[1]), through1 = through0 + e[1];
     // The reference's test is chain(p_i, i <= k) >= top with p_i = w_i / chain(w, all n ids): its two chains round by at
-    // most (k - 1) and (n - 1) units, k <= the ids above the window plus the window's; the sums here add a few hundred.
+    // most (k - 1) units (k <= the ids above the window plus the window's) and chain_terms units (see above; at most
+    // n - 1); the sums here add a few hundred.
     const double k_bound = fmin(double(a.vocab), double(info.n_before) + double(n));
-    const double rel = (k_bound + double(a.vocab) + 2.0 * kFlatWeightUlps + 512.0) * kU * a.bound_scale;
+    const double rel = (k_bound + fmin(double(a.vocab), chain_terms) + 2.0 * kFlatWeightUlps + 512.0) * kU * a.bound_scale;
     const double target_p = a.top_p * z, lo = target_p * (1.0 - rel), hi = target_p * (1.0 + rel);
     if (tid == 0) { found_at = 0x7fffffff; cut_amb = 0; }
     __syncthreads();

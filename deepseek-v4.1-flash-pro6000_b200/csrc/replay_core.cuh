@@ -263,52 +263,65 @@ __device__ double sequential_sum(ReplaySmem &s, int n, Value value) {
 
 // ---------------------------------------------------------------------------------------------------------------
 // Order of the probabilities (p descending, id ascending) without a full sort: the ids are distributed over kBuckets
-// ranges of the upper key word (one pass of counting, one of scattering), and a bucket is put in order only when the
-// top-p loop is about to reach it (one warp per bucket out of its own shared-memory area; the whole CTA for a bucket of
-// up to kTile entries).  The loop normally stops long before the tail, so most buckets are never ordered.
+// ranges of the upper key word (counted while the row is normalised, one pass of scattering), and the buckets are put
+// in order only as far as the top-p loop gets: a warp takes the buckets that begin within one run of kChunk positions
+// and sorts them together out of its own shared-memory area (buckets are ranges of the key, so whole buckets sorted
+// jointly are in their final order).  The loop normally stops long before the tail, so most buckets are never ordered.
 constexpr int kBuckets = 4096;
 constexpr int kWarpSort = 256;                       // entries a warp orders out of its own area
+constexpr int kChunk = 128;                          // positions per chunk; a chunk holds at most kChunk - 1 + its last bucket
 constexpr int kSpanCap = 96 << 20;                   // binades (2^20 upper-word steps each) the bucket grid covers
 constexpr size_t kReplayDynamicBytes = size_t(kRT / 32) * kWarpSort * 12 + size_t(kBuckets + 1) * 4;
 
 struct BucketOrder {
-  int *starts;                 // [kBuckets + 1] first position of each bucket (dynamic shared memory)
+  int *starts;                 // [kBuckets + 1] first position of each bucket (dynamic shared memory); counts before the scan
   unsigned long long *wkey;    // [warps][kWarpSort]
   int *widx;
-  int next_bucket, ordered;    // buckets before next_bucket are in order: positions [0, ordered)
+  uint32_t hi_min;             // upper key word of the largest p
+  float scale;                 // buckets per upper-word step
+  int next_chunk, ordered, n;  // chunks before next_chunk are in order: positions [0, ordered)
+  __device__ __forceinline__ int bucket_of(unsigned long long k) const {
+    const uint32_t hi = uint32_t(k >> 32), d = hi > hi_min ? hi - hi_min : 0u;
+    const float f = __uint2float_rz(d) * scale;   // monotone in the key
+    return f >= float(kBuckets - 1) ? kBuckets - 1 : int(f);
+  }
+  // first bucket whose first position is >= v (kBuckets when there is none)
+  __device__ __forceinline__ int bucket_from(int v) const {
+    int lo = 0, hi = kBuckets;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (starts[mid] >= v) hi = mid; else lo = mid + 1;
+    }
+    return lo;
+  }
 };
 
-__device__ __forceinline__ BucketOrder bucket_areas(unsigned char *dynamic) {
+__device__ __forceinline__ unsigned long long order_key(double p) { return ~(unsigned long long)__double_as_longlong(p); }
+
+// The bucket grid for probabilities between p_max and p_low (or kSpanCap below p_max; the rest shares the last bucket);
+// clears the counters.  Every thread gets the same record.
+__device__ BucketOrder bucket_begin(unsigned char *dynamic, int n, double p_max, double p_low) {
   BucketOrder b;
   b.wkey = reinterpret_cast<unsigned long long *>(dynamic);
   b.widx = reinterpret_cast<int *>(dynamic + size_t(kRT / 32) * kWarpSort * 8);
   b.starts = reinterpret_cast<int *>(dynamic + size_t(kRT / 32) * kWarpSort * 12);
-  b.next_bucket = 0; b.ordered = 0;
+  b.next_chunk = 0; b.ordered = 0; b.n = n;
+  b.hi_min = uint32_t(order_key(p_max) >> 32);
+  const uint32_t hi_low = uint32_t(order_key(p_low) >> 32);
+  uint32_t span = p_low > 0 ? (hi_low >= b.hi_min ? hi_low - b.hi_min + 1 : 1) : uint32_t(kSpanCap);
+  if (span > uint32_t(kSpanCap)) span = kSpanCap;
+  b.scale = float(kBuckets - 1) / float(span);
+  for (int i = threadIdx.x; i <= kBuckets; i += kRT) b.starts[i] = 0;
+  __syncthreads();
   return b;
 }
+__device__ __forceinline__ void bucket_count(const BucketOrder &b, double p) { atomicAdd(&b.starts[b.bucket_of(order_key(p))], 1); }
 
-// Distributes (key, id) of p[0..n) into key[] / idx[] by bucket.  p_max / p_low = (about) the largest and smallest p.
-__device__ void bucket_scatter(ReplaySmem &s, BucketOrder &b, const double *p, int n, double p_max, double p_low,
-                               unsigned long long *key, int *idx) {
-  const int tid = threadIdx.x;
-  // the grid runs from the largest p to the smallest (or kSpanCap below the largest; the rest shares the last bucket)
-  const unsigned long long lowest = p_low > 0 ? (unsigned long long)__double_as_longlong(p_low) : ~0ull;
-  const uint32_t hi_min = uint32_t((~(unsigned long long)__double_as_longlong(p_max)) >> 32);
-  const uint32_t hi_low = uint32_t((~lowest) >> 32);
-  uint32_t span = lowest == ~0ull ? uint32_t(kSpanCap) : (hi_low >= hi_min ? hi_low - hi_min + 1 : 1);
-  if (span > uint32_t(kSpanCap)) span = kSpanCap;
-  const float scale = float(kBuckets - 1) / float(span);
-  auto bucket_of = [hi_min, scale](unsigned long long k) {
-    const uint32_t hi = uint32_t(k >> 32), d = hi > hi_min ? hi - hi_min : 0u;
-    const float f = __uint2float_rz(d) * scale;   // monotone in the key
-    return f >= float(kBuckets - 1) ? kBuckets - 1 : int(f);
-  };
+// After every p has been counted: first positions from the counts, then (key, id) of p[0..n) into key[] / idx[] by bucket.
+__device__ void bucket_scatter(ReplaySmem &s, BucketOrder &b, const double *p, unsigned long long *key, int *idx) {
+  const int tid = threadIdx.x, n = b.n;
   int *count = b.starts, *cursor = reinterpret_cast<int *>(s.stage);
-  for (int i = tid; i <= kBuckets; i += kRT) count[i] = 0;
   __syncthreads();
-  for (int i = tid; i < n; i += kRT) atomicAdd(&count[bucket_of(~(unsigned long long)__double_as_longlong(p[i]))], 1);
-  __syncthreads();
-  // exclusive scan of the counts, kBuckets / kRT per thread
   constexpr int kPerThread = kBuckets / kRT;
   int mine[kPerThread], sum = 0;
 #pragma unroll
@@ -319,28 +332,40 @@ __device__ void bucket_scatter(ReplaySmem &s, BucketOrder &b, const double *p, i
   for (int r = 0; r < kPerThread; ++r) { count[tid * kPerThread + r] = at; cursor[tid * kPerThread + r] = at; at += mine[r]; }
   if (tid == 0) count[kBuckets] = n;
   __syncthreads();
-  for (int i = tid; i < n; i += kRT) {
-    const unsigned long long k = ~(unsigned long long)__double_as_longlong(p[i]);
-    const int pos = atomicAdd(&cursor[bucket_of(k)], 1);
-    key[pos] = k; idx[pos] = i;
+  for (int i0 = tid; i0 < n; i0 += 4 * kRT) {   // four independent loads in flight per thread
+    double v[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) v[r] = i0 + r * kRT < n ? p[i0 + r * kRT] : 0.0;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int i = i0 + r * kRT;
+      if (i >= n) continue;
+      const unsigned long long k = order_key(v[r]);
+      const int pos = atomicAdd(&cursor[b.bucket_of(k)], 1);
+      key[pos] = k; idx[pos] = i;
+    }
   }
   __syncthreads();
-  b.next_bucket = 0; b.ordered = 0;
 }
 
-// Puts the next buckets in order until at least `want` more positions are (or every bucket is).  Returns false when a
-// bucket is too large for the shared-memory sorts (rows with long runs of equal logits): the caller sorts the row whole.
+// Puts the next chunks in order until at least `want` more positions are (or everything is).  Returns false when a
+// chunk is too large for the shared-memory sorts (rows with long runs of equal logits): the caller sorts the row whole.
 __device__ bool bucket_order_more(ReplaySmem &s, BucketOrder &b, int want, unsigned long long *key, int *idx) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int from = b.next_bucket;
-  int to = from;
-  const int goal = b.ordered + want;
-  while (to < kBuckets && b.starts[to] < goal) ++to;   // uniform: every thread reads the same table
-  if (to == from) return true;
-  bool fits = true;
-  for (int q = from + warp; q < to; q += kRT / 32) {
-    const int st = b.starts[q], m = b.starts[q + 1] - st;
-    if (m <= 1 || m > kWarpSort) continue;
+  const int chunks = (b.n + kChunk - 1) / kChunk;
+  const int c_from = b.next_chunk;
+  const int c_to = min(chunks, c_from + (want + kChunk - 1) / kChunk);
+  if (c_to == c_from) return true;
+  if (tid == 0) s.bcast_i[2] = 0;   // chunks that are too large for a warp's area (normally none)
+  __syncthreads();
+  for (int c = c_from + warp; c < c_to; c += kRT / 32) {
+    const int q0 = b.bucket_from(c * kChunk), q1 = b.bucket_from((c + 1) * kChunk);
+    const int st = b.starts[q0], m = b.starts[q1] - st;   // (starts[kBuckets] = n)
+    if (m > kWarpSort) {
+      if (lane == 0) { const int at = atomicAdd(&s.bcast_i[2], 1); if (at < kRT / 32) s.red_i[at] = c; }
+      continue;
+    }
+    if (m <= 1) continue;
     unsigned long long *wk = b.wkey + warp * kWarpSort;
     int *wi = b.widx + warp * kWarpSort;
     int padded = 2;
@@ -362,9 +387,12 @@ __device__ bool bucket_order_more(ReplaySmem &s, BucketOrder &b, int want, unsig
     __syncwarp();
   }
   __syncthreads();
-  for (int q = from; q < to; ++q) {   // uniform: the buckets that are too large for a warp's area
-    const int st = b.starts[q], m = b.starts[q + 1] - st;
-    if (m <= kWarpSort) continue;
+  const int large = s.bcast_i[2];
+  bool fits = large <= kRT / 32;
+  for (int l = 0; l < large && fits; ++l) {   // uniform: the whole CTA orders each of them
+    const int c = s.red_i[l];
+    const int q0 = b.bucket_from(c * kChunk), q1 = b.bucket_from((c + 1) * kChunk);
+    const int st = b.starts[q0], m = b.starts[q1] - st;
     if (m > kTile) { fits = false; break; }
     int padded = kWarpSort * 2;
     while (padded < m) padded <<= 1;
@@ -385,8 +413,8 @@ __device__ bool bucket_order_more(ReplaySmem &s, BucketOrder &b, int want, unsig
     __syncthreads();
   }
   if (!fits) return false;
-  b.next_bucket = to;
-  b.ordered = b.starts[to];
+  b.next_chunk = c_to;
+  b.ordered = c_to >= chunks ? b.n : b.starts[b.bucket_from(c_to * kChunk)];
   __syncthreads();
   return true;
 }
@@ -437,19 +465,24 @@ __device__ Replayed replay_probabilities(ReplaySmem &s, const float *x, int n, d
   for (int i = tid; i < n; i += kRT) p[i] = exp_nonpos((double(x[i]) - xb) / t);
   __syncthreads();
   const double z = sequential_sum(s, n, [p](int i) { return p[i]; });
-  for (int i = tid; i < n; i += kRT) p[i] /= z;
+  bool bucketed = dynamic != nullptr && top < 1.0;
+  BucketOrder b{};
+  if (bucketed) b = bucket_begin(dynamic, n, 1.0 / z, exp_nonpos((double(low) - xb) / t) / z);
+  for (int i = tid; i < n; i += kRT) {
+    const double v = p[i] / z;
+    p[i] = v;
+    if (bucketed) bucket_count(b, v);
+  }
   __syncthreads();
   if (top < 1.0) {
     // order: p descending, id ascending (positive doubles order like their bit patterns); mass += p[idx[k++]] while
     // k < n and mass < top
     SeqResult c{-1, 0.0, 0.0};
-    bool bucketed = dynamic != nullptr;
     if (bucketed) {
-      BucketOrder b = bucket_areas(dynamic);
-      bucket_scatter(s, b, p, n, 1.0 / z, exp_nonpos((double(low) - xb) / t) / z, key, idx);
+      bucket_scatter(s, b, p, key, idx);
       int done = 0;
       while (done < n && c.found < 0) {
-        if (!bucket_order_more(s, b, 2 * kSumTile, key, idx)) { bucketed = false; break; }
+        if (!bucket_order_more(s, b, 4 * kSumTile, key, idx)) { bucketed = false; break; }
         c = exact_sequential(s, b.ordered, [p, idx](int i) { return p[idx[i]]; },
                              [top](double mass) { return !(mass < top); }, done, c.acc);
         done = b.ordered;
