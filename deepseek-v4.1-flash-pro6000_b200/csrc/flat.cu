@@ -552,39 +552,38 @@ __global__ void __launch_bounds__(kFT) flat_resolve_kernel(FlatArgs a) {
     while (padded < n) padded <<= 1;
     for (int i = tid; i < padded; i += kFT) keys[i] = i < n ? a.s.lkeys[size_t(row) * kFlatList + i] : ~0ull;
     __syncthreads();
-    if (padded <= kFT) {
-      // bitonic network, one key per thread: partners closer than a warp exchange by shuffle, the others through
-      // shared memory
-      unsigned long long key = tid < padded ? keys[tid] : ~0ull;
+    {
+      // bitonic network, two adjacent keys per thread (positions 2 tid, 2 tid + 1): partners at distance 1 are in the
+      // same thread, up to distance 32 in the same warp (shuffles), only the wider ones go through shared memory
+      const bool live = 2 * tid < padded;
+      unsigned long long k0 = live ? keys[2 * tid] : ~0ull, k1 = live ? keys[2 * tid + 1] : ~0ull;
+      const int i0 = 2 * tid;
       for (int k = 2; k <= padded; k <<= 1) {
+        const bool up = (i0 & k) == 0;   // (bit 0 of the position plays no part for k >= 2)
         for (int jj = k >> 1; jj > 0; jj >>= 1) {
-          unsigned long long other;
-          if (jj < 32) {
-            other = __shfl_xor_sync(0xffffffffu, key, jj);
+          if (jj == 1) {
+            if ((k0 > k1) == up) { const unsigned long long t = k0; k0 = k1; k1 = t; }
+            continue;
+          }
+          unsigned long long o0, o1;
+          if (jj <= 32) {
+            o0 = __shfl_xor_sync(0xffffffffu, k0, jj >> 1);
+            o1 = __shfl_xor_sync(0xffffffffu, k1, jj >> 1);
           } else {
-            keys[tid] = key;
             __syncthreads();
-            other = keys[tid ^ jj];
+            if (live) { keys[i0] = k0; keys[i0 + 1] = k1; }
             __syncthreads();
+            o0 = live ? keys[i0 ^ jj] : ~0ull;
+            o1 = live ? keys[(i0 + 1) ^ jj] : ~0ull;
           }
-          const bool keep_min = ((tid & jj) == 0) == ((tid & k) == 0);
-          key = keep_min ? (key < other ? key : other) : (key < other ? other : key);
+          const bool keep_min = ((i0 & jj) == 0) == up;
+          k0 = keep_min ? (k0 < o0 ? k0 : o0) : (k0 < o0 ? o0 : k0);
+          k1 = keep_min ? (k1 < o1 ? k1 : o1) : (k1 < o1 ? o1 : k1);
         }
       }
-      keys[tid] = key;
       __syncthreads();
-    } else {
-      for (int k = 2; k <= padded; k <<= 1) {
-        for (int jj = k >> 1; jj > 0; jj >>= 1) {
-          for (int i = tid; i < padded / 2; i += kFT) {
-            const int lo_i = ((i / jj) * 2 * jj) + (i % jj), hi_i = lo_i + jj;
-            const bool up = (lo_i & k) == 0;
-            const unsigned long long p = keys[lo_i], q = keys[hi_i];
-            if ((p > q) == up) { keys[lo_i] = q; keys[hi_i] = p; }
-          }
-          __syncthreads();
-        }
-      }
+      if (live) { keys[i0] = k0; keys[i0 + 1] = k1; }
+      __syncthreads();
     }
     // FP64 weights in sorted order and their prefix sums from the mass before the window
     double e[2];
