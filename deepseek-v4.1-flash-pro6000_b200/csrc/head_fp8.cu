@@ -128,6 +128,22 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
 }
 
+// Two fp32 fused multiply-adds in one instruction (fma.rn.f32x2: each half is the same correctly rounded FMA as
+// fmaf): the promotion of a K block is 32 or 64 of them per thread, and the epilogue warps' issue slots are what the
+// tensor pipe ends up waiting for.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+  unsigned long long v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ void fma2_acc(float &s0, float &s1, uint32_t d0, uint32_t d1, unsigned long long scale2) {
+  unsigned long long d, c, out;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(d0), "r"(d1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(c) : "f"(s0), "f"(s1));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(out) : "l"(d), "l"(scale2), "l"(c));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(s0), "=f"(s1) : "l"(out));
+}
+
 // kRows batch rows x kVocab vocabulary ids per output tile (kVocab = UMMA N: 128, or 256 to halve the activation
 // traffic per output element when the batch is large and the kernel is bound by L2 -> shared-memory copies)
 template <int kRows, int kVocab>
@@ -329,6 +345,7 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         if (!alive) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const float scale = sa[kb * kRows + (row < kRows ? row : 0)] * w_next;
+        const unsigned long long scale2 = pack2(scale, scale);
         if (kb + 1 < kblocks) w_next = __ldg(wsc + kb + 1);
         if constexpr (kMyCols == 32) {
           uint32_t r[32];
@@ -339,7 +356,7 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[acc]);
 #pragma unroll
-          for (int c = 0; c < 32; ++c) sum[c] = fmaf(__uint_as_float(r[c]), scale, sum[c]);
+          for (int c = 0; c < 32; c += 2) fma2_acc(sum[c], sum[c + 1], r[c], r[c + 1], scale2);
         } else {
           // 64 columns per thread: four 16-column loads, one in flight at a time (the register budget of 576 threads)
 #pragma unroll
@@ -353,7 +370,7 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
               if (lane == 0) mbar_arrive(&acc_empty[acc]);
             }
 #pragma unroll
-            for (int c = 0; c < 16; ++c) sum[c0 + c] = fmaf(__uint_as_float(r[c]), scale, sum[c0 + c]);
+            for (int c = 0; c < 16; c += 2) fma2_acc(sum[c0 + c], sum[c0 + c + 1], r[c], r[c + 1], scale2);
           }
         }
         if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1; }
