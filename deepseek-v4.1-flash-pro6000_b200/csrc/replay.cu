@@ -12,8 +12,9 @@
 // the host library's in the last place, which moves a sum by a few 2^-53 relative instead of by vocab * 2^-53.  A
 // decision that is still closer than 16 * 2^-53 to its threshold keeps its status bit; every other replayed row
 // leaves with status 0.  The sums follow the reference's chain of roundings exactly but in parallel (integer prefix sums
-// inside each binade of the accumulator, replay_core.cuh), and only the part of the order that the top-p loop reaches is
-// sorted, so a row costs a few hundred microseconds; the parallel bound flags a few rows in 10^5.
+// inside each binade of the accumulator, replay_core.cuh), and the order is never put together: the top-p loop consumes
+// whole ranges of the key as integer sums and sorts only the few chunks in which it needs the terms one by one.  A
+// full-vocabulary row costs a little under a millisecond; the parallel bound flags a few rows in 10^5.
 #include "replay_core.cuh"
 #include <atomic>
 

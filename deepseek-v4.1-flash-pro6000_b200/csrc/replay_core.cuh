@@ -17,6 +17,7 @@ struct ReplaySmem {
   unsigned long long key[kTile];
   int idx[kTile];
   unsigned long long scan[kRT / 32];
+  unsigned long long quick[2][kRT / 32];
   float red_f[kRT / 32];
   int red_i[kRT / 32];
   double bcast_d[4];
@@ -85,6 +86,7 @@ __device__ void sort_pairs(ReplaySmem &s, unsigned long long *key, int *idx) {
 // reference's operation), and the scan restarts behind it with the new acc.  A whole pass costs one block scan per tile
 // plus one per binade crossed (a few dozen), instead of one dependent addition per term on a single thread.
 // Terms that are negative, NaN or infinite (rows a caller passed in without validation) take the literal loop.
+constexpr int kSeqHead = 256;               // terms of a chain from zero that one thread adds literally
 constexpr int kSumPer = 4;                 // consecutive terms a thread holds in registers
 constexpr int kSumTile = kSumPer * kRT;    // terms scanned at a time
 constexpr unsigned long long kTwo52 = 1ull << 52, kTwo53 = 1ull << 53;
@@ -151,21 +153,71 @@ __device__ __forceinline__ unsigned long long block_exclusive_u64(ReplaySmem &s,
 // (first, acc0): the loop resumed at term `first` with the acc the earlier terms left.
 template <class Value, class Stop>
 __device__ SeqResult exact_sequential(ReplaySmem &s, int n, Value value, Stop stop, int first = 0, double acc0 = 0.0) {
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   double acc = acc0;         // the same in every thread
-  for (int base = first; base < n; base += kSumTile) {
+  int start = first;
+  if (first == 0 && acc0 == 0.0) {
+    // A chain that starts from zero leaves a binade with almost every one of its first terms: those are added as the
+    // reference adds them, by one thread, out of shared memory.
+    const int head = min(n, kSeqHead);
+    if (tid < head) s.stage[tid] = value(tid);
+    __syncthreads();
+    if (tid == 0) {
+      int found = -1;
+      double a = 0.0, before = 0.0;
+      for (int i = 0; i < head; ++i) {
+        before = a;
+        a += s.stage[i];
+        if (stop(a)) { found = i; break; }
+      }
+      s.bcast_i[0] = found; s.bcast_d[0] = a; s.bcast_d[1] = before;
+    }
+    __syncthreads();
+    const int found = s.bcast_i[0];
+    acc = s.bcast_d[0];
+    const double before = s.bcast_d[1];
+    __syncthreads();
+    if (found >= 0) return SeqResult{found, acc, before};
+    start = head;
+  }
+  int parity = 0;
+  for (int base = start; base < n; base += kSumTile) {
     const int m = min(kSumTile, n - base);
     // every thread keeps kSumPer consecutive terms in registers
     double v[kSumPer];
     int bad = 0;
+    {
+      // A first look at the tile as a whole: if no term is invalid or ties, and the chain neither leaves its binade nor
+      // stops by the tile's end, the tile is one integer sum (one barrier).
+      int be0;
+      unsigned long long s00, quick = 0;
+      split_double(acc, be0, s00);
+      int tied = 0;
 #pragma unroll
-    for (int r = 0; r < kSumPer; ++r) {
-      const int i = tid * kSumPer + r;
-      v[r] = i < m ? value(base + i) : 0.0;
-      bad |= !(v[r] >= 0.0 && v[r] < CUDART_INF);
+      for (int r = 0; r < kSumPer; ++r) {
+        const int i = tid * kSumPer + r;
+        v[r] = i < m ? value(base + i) : 0.0;
+        bad |= !(v[r] >= 0.0 && v[r] < CUDART_INF);
+        bool tie;
+        quick += to_units(v[r], be0, &tie);
+        tied |= tie ? 1 : 0;
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) quick += __shfl_xor_sync(0xffffffffu, quick, o);
+      if (lane == 0) s.quick[parity][warp] = quick;
+      if (tid == 0) { s.bcast_i[0] = 0x7fffffff; s.bcast_i[1] = 0x7fffffff; }
+      const int any = __syncthreads_or(bad | tied);
+      unsigned long long total = 0;
+#pragma unroll
+      for (int w = 0; w < kRT / 32; ++w) total += s.quick[parity][w];
+      parity ^= 1;
+      const unsigned long long through = s00 + total;
+      if (!any && through < kTwo53 && !stop(join_double(through, be0))) {
+        acc = join_double(through, be0);
+        continue;
+      }
+      if (any) bad = __syncthreads_or(bad);   // (uniform: `any` is the same in every thread)
     }
-    if (tid == 0) { s.bcast_i[0] = 0x7fffffff; s.bcast_i[1] = 0x7fffffff; }
-    bad = __syncthreads_or(bad);
     if (bad) {   // the literal loop, one thread
       if (tid == 0) {
         int found = -1;
@@ -279,7 +331,7 @@ struct BucketOrder {
   int *widx;
   uint32_t hi_min;             // upper key word of the largest p
   float scale;                 // buckets per upper-word step
-  int next_chunk, ordered, n;  // chunks before next_chunk are in order: positions [0, ordered)
+  int n;                       // entries
   __device__ __forceinline__ int bucket_of(unsigned long long k) const {
     const uint32_t hi = uint32_t(k >> 32), d = hi > hi_min ? hi - hi_min : 0u;
     const float f = __uint2float_rz(d) * scale;   // monotone in the key
@@ -305,7 +357,7 @@ __device__ BucketOrder bucket_begin(unsigned char *dynamic, int n, double p_max,
   b.wkey = reinterpret_cast<unsigned long long *>(dynamic);
   b.widx = reinterpret_cast<int *>(dynamic + size_t(kRT / 32) * kWarpSort * 8);
   b.starts = reinterpret_cast<int *>(dynamic + size_t(kRT / 32) * kWarpSort * 12);
-  b.next_chunk = 0; b.ordered = 0; b.n = n;
+  b.n = n;
   b.hi_min = uint32_t(order_key(p_max) >> 32);
   const uint32_t hi_low = uint32_t(order_key(p_low) >> 32);
   uint32_t span = p_low > 0 ? (hi_low >= b.hi_min ? hi_low - b.hi_min + 1 : 1) : uint32_t(kSpanCap);
@@ -348,75 +400,120 @@ __device__ void bucket_scatter(ReplaySmem &s, BucketOrder &b, const double *p, u
   __syncthreads();
 }
 
-// Puts the next chunks in order until at least `want` more positions are (or everything is).  Returns false when a
-// chunk is too large for the shared-memory sorts (rows with long runs of equal logits): the caller sorts the row whole.
-__device__ bool bucket_order_more(ReplaySmem &s, BucketOrder &b, int want, unsigned long long *key, int *idx) {
+// One chunk (the buckets that begin within positions [c * kChunk, (c + 1) * kChunk)): first position and length.
+__device__ __forceinline__ void chunk_range(const BucketOrder &b, int c, int *st, int *m) {
+  const int q0 = b.bucket_from(c * kChunk), q1 = b.bucket_from((c + 1) * kChunk);
+  *st = b.starts[q0];
+  *m = b.starts[q1] - *st;   // (starts[kBuckets] = n)
+}
+
+// Puts positions [st, st + m) of key[] / idx[] in order: warp 0 out of its shared-memory area, or the whole CTA for up
+// to kTile entries.  Called by every thread; false when the range is too large (long runs of equal logits).
+__device__ bool order_range(ReplaySmem &s, const BucketOrder &b, int st, int m, unsigned long long *key, int *idx) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int chunks = (b.n + kChunk - 1) / kChunk;
-  const int c_from = b.next_chunk;
-  const int c_to = min(chunks, c_from + (want + kChunk - 1) / kChunk);
-  if (c_to == c_from) return true;
-  if (tid == 0) s.bcast_i[2] = 0;   // chunks that are too large for a warp's area (normally none)
-  __syncthreads();
-  for (int c = c_from + warp; c < c_to; c += kRT / 32) {
-    const int q0 = b.bucket_from(c * kChunk), q1 = b.bucket_from((c + 1) * kChunk);
-    const int st = b.starts[q0], m = b.starts[q1] - st;   // (starts[kBuckets] = n)
-    if (m > kWarpSort) {
-      if (lane == 0) { const int at = atomicAdd(&s.bcast_i[2], 1); if (at < kRT / 32) s.red_i[at] = c; }
-      continue;
+  if (m > kTile) return false;
+  if (m <= 1) return true;
+  int padded = 2;
+  while (padded < m) padded <<= 1;
+  if (m <= kWarpSort) {
+    if (warp == 0) {
+      unsigned long long *wk = b.wkey;
+      int *wi = b.widx;
+      for (int i = lane; i < padded; i += 32) { wk[i] = i < m ? key[st + i] : ~0ull; wi[i] = i < m ? idx[st + i] : 0x7fffffff; }
+      __syncwarp();
+      for (int k = 2; k <= padded; k <<= 1)
+        for (int jj = k >> 1; jj > 0; jj >>= 1) {
+          for (int i = lane; i < padded / 2; i += 32) {
+            const int lo = ((i & ~(jj - 1)) << 1) | (i & (jj - 1)), hi = lo + jj;   // jj is a power of two
+            const bool up = (lo & k) == 0;
+            const unsigned long long ka = wk[lo], kb = wk[hi];
+            const int ia = wi[lo], ib = wi[hi];
+            if (key_less(kb, ib, ka, ia) == up) { wk[lo] = kb; wk[hi] = ka; wi[lo] = ib; wi[hi] = ia; }
+          }
+          __syncwarp();
+        }
+      for (int i = lane; i < m; i += 32) { key[st + i] = wk[i]; idx[st + i] = wi[i]; }
     }
-    if (m <= 1) continue;
-    unsigned long long *wk = b.wkey + warp * kWarpSort;
-    int *wi = b.widx + warp * kWarpSort;
-    int padded = 2;
-    while (padded < m) padded <<= 1;
-    for (int i = lane; i < padded; i += 32) { wk[i] = i < m ? key[st + i] : ~0ull; wi[i] = i < m ? idx[st + i] : 0x7fffffff; }
-    __syncwarp();
-    for (int k = 2; k <= padded; k <<= 1)
-      for (int jj = k >> 1; jj > 0; jj >>= 1) {
-        for (int i = lane; i < padded / 2; i += 32) {
-          const int lo = ((i & ~(jj - 1)) << 1) | (i & (jj - 1)), hi = lo + jj;   // jj is a power of two
-          const bool up = (lo & k) == 0;
-          const unsigned long long ka = wk[lo], kb = wk[hi];
-          const int ia = wi[lo], ib = wi[hi];
-          if (key_less(kb, ib, ka, ia) == up) { wk[lo] = kb; wk[hi] = ka; wi[lo] = ib; wi[hi] = ia; }
-        }
-        __syncwarp();
-      }
-    for (int i = lane; i < m; i += 32) { key[st + i] = wk[i]; idx[st + i] = wi[i]; }
-    __syncwarp();
+    __syncthreads();
+    return true;
   }
+  for (int i = tid; i < padded; i += kRT) { s.key[i] = i < m ? key[st + i] : ~0ull; s.idx[i] = i < m ? idx[st + i] : 0x7fffffff; }
   __syncthreads();
-  const int large = s.bcast_i[2];
-  bool fits = large <= kRT / 32;
-  for (int l = 0; l < large && fits; ++l) {   // uniform: the whole CTA orders each of them
-    const int c = s.red_i[l];
-    const int q0 = b.bucket_from(c * kChunk), q1 = b.bucket_from((c + 1) * kChunk);
-    const int st = b.starts[q0], m = b.starts[q1] - st;
-    if (m > kTile) { fits = false; break; }
-    int padded = kWarpSort * 2;
-    while (padded < m) padded <<= 1;
-    for (int i = tid; i < padded; i += kRT) { s.key[i] = i < m ? key[st + i] : ~0ull; s.idx[i] = i < m ? idx[st + i] : 0x7fffffff; }
-    __syncthreads();
-    for (int k = 2; k <= padded; k <<= 1)
-      for (int jj = k >> 1; jj > 0; jj >>= 1) {
-        for (int i = tid; i < padded / 2; i += kRT) {
-          const int lo = ((i & ~(jj - 1)) << 1) | (i & (jj - 1)), hi = lo + jj;
-          const bool up = (lo & k) == 0;
-          const unsigned long long ka = s.key[lo], kb = s.key[hi];
-          const int ia = s.idx[lo], ib = s.idx[hi];
-          if (key_less(kb, ib, ka, ia) == up) { s.key[lo] = kb; s.key[hi] = ka; s.idx[lo] = ib; s.idx[hi] = ia; }
-        }
-        __syncthreads();
+  for (int k = 2; k <= padded; k <<= 1)
+    for (int jj = k >> 1; jj > 0; jj >>= 1) {
+      for (int i = tid; i < padded / 2; i += kRT) {
+        const int lo = ((i & ~(jj - 1)) << 1) | (i & (jj - 1)), hi = lo + jj;
+        const bool up = (lo & k) == 0;
+        const unsigned long long ka = s.key[lo], kb = s.key[hi];
+        const int ia = s.idx[lo], ib = s.idx[hi];
+        if (key_less(kb, ib, ka, ia) == up) { s.key[lo] = kb; s.key[hi] = ka; s.idx[lo] = ib; s.idx[hi] = ia; }
       }
-    for (int i = tid; i < m; i += kRT) { key[st + i] = s.key[i]; idx[st + i] = s.idx[i]; }
-    __syncthreads();
-  }
-  if (!fits) return false;
-  b.next_chunk = c_to;
-  b.ordered = c_to >= chunks ? b.n : b.starts[b.bucket_from(c_to * kChunk)];
+      __syncthreads();
+    }
+  for (int i = tid; i < m; i += kRT) { key[st + i] = s.key[i]; idx[st + i] = s.idx[i]; }
   __syncthreads();
   return true;
+}
+
+// The reference's loop `mass += p[idx[k++]] while k < n && mass < top` over the stable order, without putting the order
+// together first.  Inside one binade of the accumulator (and without exact ties) the chain adds rn(x / U) per term
+// whatever the order of the terms, so a chunk -- whole buckets, i.e. a range of the key, unordered inside -- is consumed
+// by one integer sum as long as the chain neither leaves the binade nor stops inside it; the warps take 32 chunks at a
+// time.  Only a chunk in which that happens (a few dozen per row, and the one where the loop stops) is put in order and
+// walked term by term.  found = the loop's k - 1 (a position of the order); key[found] / idx[found] are then in place.
+// ok = false: a chunk was too large to order here.
+template <class Stop>
+__device__ SeqResult chain_over_chunks(ReplaySmem &s, const BucketOrder &b, const double *p, unsigned long long *key,
+                                       int *idx, Stop stop, bool *ok) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int kW = kRT / 32;
+  const int chunks = (b.n + kChunk - 1) / kChunk;
+  double acc = 0.0;
+  *ok = true;
+  int c = 0;
+  while (c < chunks) {
+    int be;
+    unsigned long long s0;
+    split_double(acc, be, s0);
+    // one chunk per warp: integer sum of its terms at the accumulator's spacing, and whether any of them ties
+    unsigned long long sum = 0;
+    int tie = 0;
+    if (c + warp < chunks) {
+      int st, m;
+      chunk_range(b, c + warp, &st, &m);
+      for (int j = lane; j < m; j += 32) {
+        bool t;
+        sum += to_units(p[idx[st + j]], be, &t);
+        tie |= t ? 1 : 0;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      tie |= __shfl_xor_sync(0xffffffffu, tie, o);
+    }
+    if (lane == 0) { s.scan[warp] = sum; s.red_i[warp] = tie; }
+    __syncthreads();
+    // every thread walks the (at most 32) chunk sums: the first chunk that needs its terms one by one
+    unsigned long long units = s0;
+    int special = -1;
+    for (int w = 0; w < kW && c + w < chunks; ++w) {
+      const unsigned long long through = units + s.scan[w];
+      if (s.red_i[w] || through >= kTwo53 || stop(join_double(through, be))) { special = w; break; }
+      units = through;
+    }
+    __syncthreads();   // scan[] / red_i[] are rewritten by the next round (and by the walk below)
+    acc = join_double(units, be);   // the chunks before the special one are consumed
+    if (special < 0) { c += kW; continue; }
+    int st, m;
+    chunk_range(b, c + special, &st, &m);
+    if (!order_range(s, b, st, m, key, idx)) { *ok = false; return SeqResult{-1, acc, acc}; }
+    const SeqResult r = exact_sequential(s, st + m, [p, idx](int i) { return p[idx[i]]; }, stop, st, acc);
+    if (r.found >= 0) return r;
+    acc = r.acc;
+    c += special + 1;
+  }
+  return SeqResult{-1, acc, acc};
 }
 
 // largest value over the block, to every thread
@@ -480,13 +577,9 @@ __device__ Replayed replay_probabilities(ReplaySmem &s, const float *x, int n, d
     SeqResult c{-1, 0.0, 0.0};
     if (bucketed) {
       bucket_scatter(s, b, p, key, idx);
-      int done = 0;
-      while (done < n && c.found < 0) {
-        if (!bucket_order_more(s, b, 4 * kSumTile, key, idx)) { bucketed = false; break; }
-        c = exact_sequential(s, b.ordered, [p, idx](int i) { return p[idx[i]]; },
-                             [top](double mass) { return !(mass < top); }, done, c.acc);
-        done = b.ordered;
-      }
+      bool fits;
+      c = chain_over_chunks(s, b, p, key, idx, [top](double mass) { return !(mass < top); }, &fits);
+      if (!fits) bucketed = false;
     }
     if (!bucketed) {
       for (int i = tid; i < kReplayPad; i += kRT) {
@@ -502,8 +595,9 @@ __device__ Replayed replay_probabilities(ReplaySmem &s, const float *x, int n, d
     // how far the crossing is from flipping: the kept prefix reached top by (mass - top), the one before missed it by (top - prev)
     out.cut_margin = k >= n && mass < top ? (top - mass) / top : fmin(mass - top, top - prev) / top;
     // the rest is zeroed and every p divided by the kept mass; kept = the order's first k = everything up to the k-th pair
-    const unsigned long long cut_key = key[k - 1];
-    const int cut_id = idx[k - 1];
+    // (the loop ran through without reaching top: everything is kept)
+    const unsigned long long cut_key = c.found >= 0 ? key[k - 1] : ~0ull;
+    const int cut_id = c.found >= 0 ? idx[k - 1] : 0x7fffffff;
     __syncthreads();
     for (int i = tid; i < n; i += kRT) {
       const double v = p[i];
