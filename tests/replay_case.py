@@ -34,8 +34,12 @@ def verify_case(seqs, vocab, t, top):
     args = (cu(target), cu(draft), cu(ids.reshape(-1)), drafts, t, top, cu(seeds.view(np.int64)), cu(steps.view(np.int64)))
     res, st = pkg.verify_logits(*args)
     # the same call with room for the statistics and chunk records only: no replay, the bits stay
-    full = pkg.verify_scratch_bytes(seqs, drafts, vocab)
-    small = torch.zeros(full - 2 * 131072 * 28, dtype=torch.uint8, device=dev)
+    lib = pkg.lib()
+    lib.ds41_b200_shard_chunks.restype = __import__("ctypes").c_int
+    rows_all = seqs * (2 * drafts + 1)   # 48-byte statistics + 544-byte chunk records per row, rounded up to 16 bytes
+    streaming_only = (rows_all * 48 + rows_all * lib.ds41_b200_shard_chunks(vocab) * 544 + 15) & ~15
+    assert streaming_only < pkg.verify_scratch_bytes(seqs, drafts, vocab)
+    small = torch.zeros(streaming_only, dtype=torch.uint8, device=dev)
     res0, st0 = pkg.verify_logits(*args, scratch=small)
     torch.cuda.synchronize()
     got = pkg.results_to_numpy(res)
