@@ -163,12 +163,18 @@ def capture(torch, fn):
 class HeadSample:
     """cfg2 / cfg5: hidden -> quantise -> FP8 head (this rank's vocabulary slice) -> sampler."""
 
-    def __init__(self, pkg, torch, device, batch, rank, world, temperature=0.6, top_p=0.95, strategy="rows"):
+    def __init__(self, pkg, torch, device, batch, rank, world, temperature=0.6, top_p=0.95, strategy="rows", vocab_ranks=0):
         self.pkg, self.torch, self.device, self.B, self.rank, self.world = pkg, torch, device, batch, rank, world
         self.t, self.top_p = temperature, top_p
         from importlib import import_module
-        self.v0, self.vn = import_module("ds41_b200.sharded").shard_plan(VOCAB, world)[rank]
-        self.wq, self.ws = make_weights(torch, device, self.vn, 1234 + rank)
+        # the vocabulary is split over vocab_ranks ranks (one copy of the weights per such team; 0 = all ranks)
+        # default for the rows exchange: teams of two (measured at 4 and 8 GPUs: 0.385 / 0.273 ms per step against
+        # 0.410 / 0.305 ms with the vocabulary split over all ranks; half of a team's logits cross NVLink, not 7/8)
+        if not vocab_ranks and strategy == "rows" and world % 2 == 0:
+            vocab_ranks = 2
+        self.vocab_ranks = vocab_ranks if (vocab_ranks and world % vocab_ranks == 0 and strategy == "rows") else world
+        self.v0, self.vn = import_module("ds41_b200.sharded").shard_plan(VOCAB, self.vocab_ranks)[rank % self.vocab_ranks]
+        self.wq, self.ws = make_weights(torch, device, self.vn, 1234 + rank % self.vocab_ranks)
         g = torch.Generator(device=device).manual_seed(99)
         self.ring = [torch.randn(batch, HIDDEN, device=device, generator=g).to(torch.bfloat16) for _ in range(16)]
         self.host_ring = [h.cpu().pin_memory() for h in self.ring]
@@ -209,7 +215,8 @@ class HeadSample:
         self.launches_per_step = 8
         if world > 1:
             self.sharded = import_module("ds41_b200.sharded").ShardedDecodeTail(pkg, device, batch, self.v0, self.vn,
-                                                                              VOCAB, temperature, top_p, strategy)
+                                                                              VOCAB, temperature, top_p, strategy,
+                                                                              vocab_ranks=self.vocab_ranks)
             strategy = self.sharded.strategy  # "candidates" if the peer buffers could not be mapped
             self.exchange_note = self.sharded.exchange_error
             # rows: quantise, head (+ peer stores and the row records merged into the owners), flat_hist / window / mass /
@@ -245,7 +252,12 @@ class HeadSample:
         pkg = self.pkg
         x = self.ring[i % len(self.ring)] if hidden is None else hidden
         self.steps.add_(1)  # a fresh Philox step per decode step (spark.h:122-128)
-        pkg.quantize_activations(x, self.a, self.a_scale)
+        if self.sharded and self.sharded.exchange is not None and self.sharded.mode() == "rows":
+            ex = self.sharded.exchange     # only the rows this rank's team computes
+            sl = slice(ex.team_row0, ex.team_row0 + ex.team_rows)
+            pkg.quantize_activations(x[sl], self.a[sl], self.a_scale[sl])
+        else:
+            pkg.quantize_activations(x, self.a, self.a_scale)
         if self.sharded and captured:   # the row exchange, as ShardedDecodeTail.step issues it, without its host checks
             exch = self.sharded.exchange
             exch.head_scatter(self.a, self.a_scale, self.wq, self.ws, self.v0, self.flag)
@@ -368,10 +380,11 @@ class HeadSample:
         """Sharded run, rank 0: recompute the last step unsharded (all ranks' weight slices, one GPU) and compare the
         token ids: the sharded path must give the 1-GPU path's tokens."""
         torch, pkg = self.torch, self.pkg
-        plan = __import__("ds41_b200.sharded", fromlist=["shard_plan"]).shard_plan(VOCAB, self.world)
+        plan = __import__("ds41_b200.sharded", fromlist=["shard_plan"]).shard_plan(VOCAB, self.vocab_ranks)
         parts = [make_weights(torch, self.device, n, 1234 + r) for r, (_, n) in enumerate(plan)]
         wq = torch.cat([p[0] for p in parts]); ws = torch.cat([p[1] for p in parts])
         logits = torch.empty((self.B, VOCAB), dtype=torch.float32, device=self.device)
+        pkg.quantize_activations(self.hidden, self.a, self.a_scale)   # (a sharded step quantises its team's rows only)
         pkg.head_fp8(self.a, self.a_scale, wq, ws, logits, self.flag)
         tok, st = pkg.sample_logits(logits, self.t, self.top_p, self.seeds, self.steps, scratch=None)
         torch.cuda.synchronize()
@@ -597,14 +610,18 @@ def cpu_baseline(workload_name, budget_rows=None):
                       "in this figure"}
 
 
-def workload_config(name, world, exchange=None):
+def workload_config(name, world, exchange=None, vocab_ranks=None):
     cfg = {"workload": name, "vocab": VOCAB, "data_recipe": "the reference benchmark's configurations, seeded synthetic"}
     if name.startswith("cfg2") or name.startswith("cfg5"):
         cfg.update({"hidden": HIDDEN, "batch": int(name.split("_b")[1]), "temperature": 0.6, "top_p": 0.95,
                     "weights": "e4m3 [129280,4096] + fp32 scale per 128x128, resident in HBM",
-                    "parallelism": "1 GPU" if world == 1 else f"head vocab-sharded x{world} (128-row blocks), sampler row-sharded",
+                    "parallelism": "1 GPU" if world == 1 else
+                                   f"head vocab-sharded x{vocab_ranks or world} (128-row blocks) inside {world // (vocab_ranks or world)} "
+                                   f"team(s) of ranks, each team holding one copy of the weights and computing its own "
+                                   f"members' batch rows; sampler row-sharded over the {world} ranks",
                     "l2": "529.5 MB of weights stream from HBM every step (> 126 MB L2); hidden states cycle over 16 buffers"})
         if world > 1:
+            cfg["vocab_ranks"], cfg["teams"] = vocab_ranks or world, world // (vocab_ranks or world)
             cfg["exchange"] = {"rows": "head epilogue stores each row's slice into the row owner's buffer (peer stores), "
                                        "1-word all-reduce, all-gather of tokens",
                                "candidates": "all-gather of 544-byte chunk records, replicated combine, uncovered rows "
@@ -662,6 +679,9 @@ def main():
     ap.add_argument("--workload", default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--vocab-ranks", type=int, default=0,
+                    help="N>1, rows exchange: ranks that share one copy of the head's weights (the vocabulary is split "
+                         "over that many; the batch is split over the N / vocab-ranks teams); 0 = all N")
     ap.add_argument("--shard-exchange", default="rows", choices=["rows", "candidates", "auto"],
                     help="N>1: how the vocabulary-sharded ranks exchange (see the package's sharded.py)")
     args = ap.parse_args()
@@ -685,7 +705,8 @@ def main():
     pkg = entry.load_package()
     name = args.workload
     if name.startswith("cfg2") or name.startswith("cfg5"):
-        wl = HeadSample(pkg, torch, device, int(name.split("_b")[1]), rank, world, strategy=args.shard_exchange)
+        wl = HeadSample(pkg, torch, device, int(name.split("_b")[1]), rank, world, strategy=args.shard_exchange,
+                        vocab_ranks=args.vocab_ranks)
     elif name.startswith("cfg3"):
         wl = VerifyWorkload(pkg, torch, device)
     elif name.startswith("cfg4"):
@@ -842,7 +863,7 @@ def main():
                            "timed_ms": sum(block_ms)},
                 "scaling": "strong" if name.startswith("cfg5") else "weak", "vs_baseline": None,
                 "dtype": "e4m3 x e4m3 -> f32 (head), f32 logits / f64 sampler" if hasattr(wl, "wq") else "f32 logits, f64 sums",
-                "data": "synthetic", "config": workload_config(name, world, args.shard_exchange), "clocks": clock_info,
+                "data": "synthetic", "config": workload_config(name, world, args.shard_exchange, getattr(wl, "vocab_ranks", None)), "clocks": clock_info,
                 "e2e": {"value": units * e2e_steps / e2e_s, "unit": "sequences/s" if name.startswith("cfg3") else "tokens/s",
                         "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_s / e2e_steps * 1e3,
                         "blocks": len(e2e_ms)},

@@ -280,13 +280,24 @@ class PeerMappingUnavailable(RuntimeError):
 class RowExchange:
     """One peer-visible full-vocabulary logits buffer [rows_per_owner, vocab] per rank, mapped into every rank."""
 
-    def __init__(self, pkg, device, rows, vocab, group=None, guard=None):
+    def __init__(self, pkg, device, rows, vocab, group=None, guard=None, vocab_ranks=None):
+        """vocab_ranks: how many ranks share one copy of the head's weights (the vocabulary is split over that many;
+        default: all of them).  With fewer, the ranks form world / vocab_ranks teams that each hold a copy, and a team
+        computes only the batch rows its own members sample: less data crosses NVLink (a rank sends
+        (vocab_ranks - 1) / vocab_ranks of a [rows / teams, vocab / vocab_ranks] slice), more weight bytes are read."""
         self.pkg, self.device, self.rows, self.vocab, self.group = pkg, device, rows, vocab, group
         self.guard = guard or StepGuard(group)
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.vocab_ranks = vocab_ranks or self.world
+        if self.world % self.vocab_ranks:
+            raise ValueError("vocab_ranks must divide the number of ranks")
         self.rows_per_owner, plan = rows_plan(rows, self.world)
         self.row0, self.my_rows = plan[self.rank]
+        # this rank's team: ranks [team0, team0 + vocab_ranks); its batch rows are the ones its members own (contiguous)
+        self.team0 = (self.rank // self.vocab_ranks) * self.vocab_ranks
+        self.team_row0 = min(rows, self.team0 * self.rows_per_owner)
+        self.team_rows = min(rows, (self.team0 + self.vocab_ranks) * self.rows_per_owner) - self.team_row0
         lib = pkg.lib()
         lib.ds41_b200_peer_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]
         lib.ds41_b200_peer_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
@@ -340,7 +351,7 @@ class RowExchange:
             self.full = None
             self.close()
             raise PeerMappingUnavailable(failure)
-        self.owner_ptrs = (C.c_void_p * self.world)(*ptrs)
+        self.owner_ptrs = (C.c_void_p * self.vocab_ranks)(*ptrs[self.team0:self.team0 + self.vocab_ranks])
         self.full = torch.as_tensor(_DeviceBlock(mine.value, (self.rows_per_owner, vocab), "<f4"), device=device)
         self.full.zero_()
         self.stats = torch.as_tensor(_DeviceBlock(mine.value + self.stats_offset, (self.rows_per_owner, 16), "|u1"),
@@ -356,11 +367,17 @@ class RowExchange:
             dist.barrier(group=group)  # every buffer exists and is mapped before anyone writes
 
     def head_scatter(self, a, a_scale, w, w_scale, vocab_offset, error_flag=None):
-        """This rank's vocabulary slice of every row's logits, stored into the rows' owners."""
+        """This rank's vocabulary slice of its team's rows' logits, stored into the rows' owners.  a / a_scale: the
+        quantised activations of the whole batch (the team's rows are taken from it) or of the team's rows only."""
+        if a.shape[0] == self.rows and self.team_rows != self.rows:
+            a = a[self.team_row0:self.team_row0 + self.team_rows]
+            a_scale = a_scale[self.team_row0:self.team_row0 + self.team_rows]
         M, K = a.shape
+        if M != self.team_rows:
+            raise ValueError(f"activations of {M} rows, the team's share is {self.team_rows}")
         with torch.cuda.device(self.device):
             rc = self._lib.ds41_b200_head_fp8_scatter_stats(
-                a.data_ptr(), a_scale.data_ptr(), w.data_ptr(), w_scale.data_ptr(), self.owner_ptrs, self.world,
+                a.data_ptr(), a_scale.data_ptr(), w.data_ptr(), w_scale.data_ptr(), self.owner_ptrs, self.vocab_ranks,
                 self.rows_per_owner, self.vocab, vocab_offset, M, w.shape[0], K, self.stats_offset,
                 error_flag.data_ptr() if error_flag is not None else None,
                 C.c_void_p(torch.cuda.current_stream().cuda_stream))
@@ -417,7 +434,7 @@ class ShardedDecodeTail:
     `probe_every` steps whenever more than a quarter of the rows of a step were not covered."""
 
     def __init__(self, pkg, device, rows, vocab_offset, vocab_local, vocab, temperature, top_p, strategy="auto",
-                 group=None, probe_every=256, timeout_s=30.0):
+                 group=None, probe_every=256, timeout_s=30.0, vocab_ranks=None):
         self.pkg, self.device, self.rows, self.v0, self.vn, self.vocab = pkg, device, rows, vocab_offset, vocab_local, vocab
         self.guard = StepGuard(group, timeout_s)
         self.t, self.top_p, self.strategy, self.probe_every = temperature, top_p, strategy, probe_every
@@ -425,7 +442,7 @@ class ShardedDecodeTail:
         self.exchange, self.exchange_error = None, None
         if strategy != "candidates":
             try:
-                self.exchange = RowExchange(pkg, device, rows, vocab, group, self.guard)
+                self.exchange = RowExchange(pkg, device, rows, vocab, group, self.guard, vocab_ranks)
             except PeerMappingUnavailable as exc:  # the same on every rank: fall back to the NCCL-only exchange
                 self.exchange_error = str(exc)
                 self.strategy = strategy = "candidates"
