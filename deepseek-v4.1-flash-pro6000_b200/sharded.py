@@ -273,6 +273,17 @@ def rows_plan(rows, world):
     return per, [(min(rows, r * per), max(0, min(rows, (r + 1) * per) - min(rows, r * per))) for r in range(world)]
 
 
+def team_plan(rows, world, rank, vocab_ranks):
+    """(first rank of this rank's team, first batch row the team computes, number of such rows): the team is the
+    vocab_ranks consecutive ranks that share one copy of the head's weights, its rows are the ones its members own."""
+    if vocab_ranks < 1 or world % vocab_ranks:
+        raise ValueError("vocab_ranks must divide the number of ranks")
+    per, _ = rows_plan(rows, world)
+    team0 = (rank // vocab_ranks) * vocab_ranks
+    row0 = min(rows, team0 * per)
+    return team0, row0, min(rows, (team0 + vocab_ranks) * per) - row0
+
+
 class PeerMappingUnavailable(RuntimeError):
     """Raised on EVERY rank when some rank could not allocate or map the peer-visible buffers."""
 
@@ -290,14 +301,10 @@ class RowExchange:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.vocab_ranks = vocab_ranks or self.world
-        if self.world % self.vocab_ranks:
-            raise ValueError("vocab_ranks must divide the number of ranks")
         self.rows_per_owner, plan = rows_plan(rows, self.world)
         self.row0, self.my_rows = plan[self.rank]
         # this rank's team: ranks [team0, team0 + vocab_ranks); its batch rows are the ones its members own (contiguous)
-        self.team0 = (self.rank // self.vocab_ranks) * self.vocab_ranks
-        self.team_row0 = min(rows, self.team0 * self.rows_per_owner)
-        self.team_rows = min(rows, (self.team0 + self.vocab_ranks) * self.rows_per_owner) - self.team_row0
+        self.team0, self.team_row0, self.team_rows = team_plan(rows, self.world, self.rank, self.vocab_ranks)
         lib = pkg.lib()
         lib.ds41_b200_peer_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]
         lib.ds41_b200_peer_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]

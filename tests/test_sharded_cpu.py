@@ -149,6 +149,31 @@ def test_rows_plan_covers_every_row_once():
             assert all(first == min(rows, r * per) for r, (first, _) in enumerate(plan))
 
 
+def test_team_plan_partitions_rows_and_ranks():
+    """Teams of vocab_ranks ranks: every batch row is computed by exactly one team, namely the team of the rank that
+    owns (samples) it, and a team's rows are contiguous."""
+    sys.path.insert(0, ROOT)
+    import __graft_entry__ as entry
+    entry.load_package()
+    sh = importlib.import_module("ds41_b200.sharded")
+    for rows in (1, 7, 1000, 1024):
+        for world, vocab_ranks in ((2, 1), (2, 2), (4, 2), (8, 2), (8, 4), (8, 8), (6, 3)):
+            per, plan = sh.rows_plan(rows, world)
+            computed = []
+            for team in range(world // vocab_ranks):
+                members = range(team * vocab_ranks, (team + 1) * vocab_ranks)
+                got = {sh.team_plan(rows, world, r, vocab_ranks) for r in members}
+                assert len(got) == 1                      # every member sees the same team
+                team0, row0, n = got.pop()
+                assert team0 == team * vocab_ranks
+                owned = [r for m in members for r in range(plan[m][0], plan[m][0] + plan[m][1])]
+                assert owned == list(range(row0, row0 + n))
+                computed += owned
+            assert computed == list(range(rows))
+    with pytest.raises(ValueError):
+        sh.team_plan(16, 8, 0, 3)
+
+
 def rows_worker(rank, world, port, out, rows=7):
     """Row-sharded exchange on CPU: every rank samples its own rows (here: the oracle on full-vocabulary rows that the
     other ranks' "head slices" were written into) and publishes; everyone must end with all tokens."""
