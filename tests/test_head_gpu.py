@@ -114,6 +114,7 @@ def test_head_scatter_to_row_owners(pkg, oracle, M, owners):
     ex = sharded.RowExchange.__new__(sharded.RowExchange)  # buffers are local here: no IPC, only the launch wrapper
     ex.pkg, ex.device, ex.world, ex.rows_per_owner, ex.vocab = pkg, torch.device("cuda", 0), owners, per, N
     ex.stats_offset = stats_offset
+    ex.rows, ex.vocab_ranks, ex.team_row0, ex.team_rows = M, owners, 0, M   # one team: every "rank" computes every row
     import ctypes as C
     ex._lib = pkg.lib()
     ex._lib.ds41_b200_head_fp8_scatter_stats.argtypes = [C.c_void_p] * 4 + [C.POINTER(C.c_void_p), C.c_int, C.c_int,
