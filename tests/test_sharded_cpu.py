@@ -326,3 +326,62 @@ def test_rank_that_leaves_between_steps_stops_the_others_before_their_next_launc
         assert out[2] == {"left": True}
         for rank in (0, 1):
             assert out[rank]["raised"] and "left the group" in out[rank]["raised"], out[rank]
+
+
+class _FakeStore:
+    """Stand-in for the rendezvous store: add(key, n) returns the running count, as torch's stores do."""
+
+    def __init__(self):
+        self.counts, self.reads, self.broken = {}, 0, False
+
+    def add(self, key, n):
+        if self.broken:
+            raise RuntimeError("store connection lost")
+        self.reads += 1
+        self.counts[key] = self.counts.get(key, 0) + n
+        return self.counts[key]
+
+
+def test_step_guard_host_logic_without_a_process_group():
+    """The guard's bookkeeping on its own (no ranks, no GPU): the leave counter is read at the configured cadence, a
+    leave or a lost store stops the step before anything is launched, a collective that raises becomes
+    CollectiveFailure, and once failed the guard refuses everything."""
+    sys.path.insert(0, ROOT)
+    import __graft_entry__ as entry
+    entry.load_package()
+    sh = importlib.import_module("ds41_b200.sharded")
+    store = _FakeStore()
+    g = sh.StepGuard(None, timeout_s=1.0, check_every=4, store=store)
+    g.world = 3                                   # as if two peers existed
+    for _ in range(9):
+        g.before_step()
+    assert store.reads == 3                       # steps 1, 5, 9
+    store.counts["ds41_b200/left"] = 1            # a peer announced that it stops
+    for _ in range(3):
+        g.before_step()                           # steps 10-12: not a check step yet
+    with pytest.raises(sh.CollectiveFailure, match="left the group"):
+        g.before_step()                           # step 13
+    with pytest.raises(sh.CollectiveFailure, match="earlier"):
+        g.before_step()
+    with pytest.raises(sh.CollectiveFailure):
+        g.collective("anything", lambda: None)
+
+    g2 = sh.StepGuard(None, timeout_s=1.0, check_every=1, store=store)
+    g2.world = 2
+    store.counts.clear()
+    g2.before_step()
+    def boom():
+        raise RuntimeError("connection reset by peer")
+    with pytest.raises(sh.CollectiveFailure, match="token all-gather: connection reset"):
+        g2.collective("token all-gather", boom)
+    assert g2.failed
+
+    g3 = sh.StepGuard(None, timeout_s=1.0, check_every=1, store=store)
+    g3.world = 2
+    store.broken = True                           # the store lives on rank 0: unreachable means rank 0 is gone
+    with pytest.raises(sh.CollectiveFailure, match="rendezvous store"):
+        g3.before_step()
+    g4 = sh.StepGuard(None, timeout_s=1.0, check_every=1, store=None)
+    g4.before_step()                              # a single rank: nothing to watch
+    g4.collective("none", lambda: None)
+    g4.finish()
