@@ -546,7 +546,7 @@ class PenaltyWorkload:
         assert (self.status.cpu().numpy() >= 0).all()
 
 
-def cpu_baseline(workload_name, budget_rows=None):
+def cpu_baseline(workload_name, sample_rows=None):
     """Times the reference's own host sampling rule (oracle/_ref when it was compiled here, else this repository's
     port) on the host cores: a bounded sample of the workload's logits rows, one row per thread at a time."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
@@ -589,7 +589,7 @@ def cpu_baseline(workload_name, budget_rows=None):
         dt = time.perf_counter() - t0
         return {"value": rows / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
                 "sample": f"{rows} rows; penalties/bitmask/top-k have no reference code, so this is the repository's CPU rule"}
-    rows = budget_rows or max(64, 4 * cores)
+    rows = sample_rows or max(64, 4 * cores)
     # logits with the distribution the FP8 head produces on this recipe: N(0, (0.02 * sqrt(4096))^2) = N(0, 1.28^2)
     x = orc.gen_normal(2, 0, (min(rows, 64), VOCAB), 1.28)
     x = np.concatenate([x] * ((rows + x.shape[0] - 1) // x.shape[0]))[:rows]

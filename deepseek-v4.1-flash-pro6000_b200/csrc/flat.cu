@@ -364,7 +364,7 @@ static __device__ const double kPow2Neg64[64] = {
 // has 64 entries (512 bytes, four rows of shared memory) so that a warp's 32 lookups cost few wavefronts.  Error of a
 // weight: 360 * 2^-53 from the truncation, 2 X ln 2 * 2^-53 from the roundings of max - y and of the product, 1.5 ulp from
 // the table entry and the polynomial's arithmetic: below kFlatWeightUlps * 2^-53 for X <= kFlatMaxExponent, which the
-// resolve kernel's bounds budget.  Ten FP64 instructions with the two accumulations, none of them a branch.
+// resolve kernel's bounds allow for.  Ten FP64 instructions with the two accumulations, none of them a branch.
 constexpr double kFlatWeightUlps = 1024.0;
 struct WeightRow {     // per-row constants of the weight routine
   float m, k32;        // maximum; 64 * log2(e)/T

@@ -358,7 +358,7 @@ head_fp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
           for (int c = 0; c < 32; c += 2) fma2_acc(sum[c], sum[c + 1], r[c], r[c + 1], scale2);
         } else {
-          // 64 columns per thread: four 16-column loads, one in flight at a time (the register budget of 576 threads)
+          // 64 columns per thread: four 16-column loads, one in flight at a time (what the registers of 576 threads leave room for)
 #pragma unroll
           for (int c0 = 0; c0 < kMyCols; c0 += 16) {
             uint32_t r[32];

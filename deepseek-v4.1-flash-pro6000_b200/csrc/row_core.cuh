@@ -87,7 +87,7 @@ struct Slot {  // one CTA's contribution to a cluster-wide exchange
 // polynomial (truncation < 3e-20), the reduction with ln2/64 split into a 32-bit head and a tail so that n * head is
 // exact.  Error: half an ulp from the table entry, half an ulp from the final fused multiply-add, < 0.01 ulp from the
 // rest: below 1.01 ulp, i.e. a relative error < 2.1 * 2^-53, which the decision bounds of every caller allow for
-// (they budget tens of units per weight).  Results below the normal range (x < -708) are returned as 0: such a weight
+// (they allow tens of units per weight).  Results below the normal range (x < -708) are returned as 0: such a weight
 // is < 1e-307 of the row's largest, which no comparison made on the sums can see.  12 FP64 instructions against the
 // library routine's ~47.
 static __device__ const double kExp2Table[64] = {
@@ -155,7 +155,7 @@ struct __align__(128) RowSmem {
   int red_i[kWarps];
   int red_j[kWarps];
   unsigned long long red_q[kWarps];
-  Slot verdict;
+  Slot outcome;
   unsigned long long mbar;
   unsigned long long bcast_q;
   int list_count;
@@ -662,7 +662,7 @@ __device__ CutResult find_cut(RowCtx &c, float max_logit, float first_width, int
       out.ambiguous = amb;
       return out;
     }
-    Slot verdict{};
+    Slot outcome{};
     double *sorted_e = reinterpret_cast<double *>(s->bin_mass);  // local bins are dead once the totals exist
     if (c.rank == 0) {
       const int n = chosen == -2 ? 0 : min(s->list_count, kListCap);
@@ -709,22 +709,22 @@ __device__ CutResult find_cut(RowCtx &c, float max_logit, float first_width, int
             }
           }
         }
-        verdict.i[0] = direction;
-        verdict.i[1] = amb;
+        outcome.i[0] = direction;
+        outcome.i[1] = amb;
         if (direction == 0) {
           const bool all_kept = chosen == -2 || pos < 0 || (pos == n - 1 && n_after == 0);
-          verdict.f[0] = all_kept ? -CUDART_INF_F : s->u.w.sorted_y[pos];
-          verdict.i[2] = all_kept ? -1 : s->u.w.sorted_id[pos];
-          verdict.i[3] = all_kept ? n_before + n : n_before + pos + 1;
-          verdict.d[0] = mass;
+          outcome.f[0] = all_kept ? -CUDART_INF_F : s->u.w.sorted_y[pos];
+          outcome.i[2] = all_kept ? -1 : s->u.w.sorted_id[pos];
+          outcome.i[3] = all_kept ? n_before + n : n_before + pos + 1;
+          outcome.d[0] = mass;
         }
-        s->verdict = verdict;
+        s->outcome = outcome;
       }
       __syncthreads();
-      verdict = s->verdict;
+      outcome = s->outcome;
       __syncthreads();
     }
-    const Slot v = exchange(c, verdict)[0];
+    const Slot v = exchange(c, outcome)[0];
     if (v.i[0] == 0) {
       out.cut.y = v.f[0]; out.cut.id = v.i[2]; out.kept = v.i[3]; out.e_kept = v.d[0]; out.ambiguous = v.i[1];
       return out;

@@ -156,7 +156,7 @@ __device__ inline FastOutcome fast_small_support(RowCtx &c, float max_logit, dou
     __syncthreads();
     const int found = s->bcast_i[0], through = s->bcast_i[1];
     __syncthreads();
-    if (found < 0 || through > kListCap) { out.applicable = 0; return out; }  // same verdict in every CTA
+    if (found < 0 || through > kListCap) { out.applicable = 0; return out; }  // same outcome in every CTA
     pick = found;
   }
 
@@ -266,12 +266,12 @@ __device__ inline FastOutcome fast_small_support(RowCtx &c, float max_logit, dou
       out.token = token;
     }
     out.status = status;
-    s->verdict.i[0] = out.token; s->verdict.i[1] = out.status; s->verdict.i[2] = out.kept; s->verdict.i[3] = out.cut.id;
-    s->verdict.f[0] = out.cut.y; s->verdict.d[0] = out.z; s->verdict.d[1] = out.e_kept;
+    s->outcome.i[0] = out.token; s->outcome.i[1] = out.status; s->outcome.i[2] = out.kept; s->outcome.i[3] = out.cut.id;
+    s->outcome.f[0] = out.cut.y; s->outcome.d[0] = out.z; s->outcome.d[1] = out.e_kept;
   }
   __syncthreads();
-  out.token = s->verdict.i[0]; out.status = s->verdict.i[1]; out.kept = s->verdict.i[2]; out.cut.id = s->verdict.i[3];
-  out.cut.y = s->verdict.f[0]; out.z = s->verdict.d[0]; out.e_kept = s->verdict.d[1];
+  out.token = s->outcome.i[0]; out.status = s->outcome.i[1]; out.kept = s->outcome.i[2]; out.cut.id = s->outcome.i[3];
+  out.cut.y = s->outcome.f[0]; out.z = s->outcome.d[0]; out.e_kept = s->outcome.d[1];
   out.entered = count_mode ? top_k : allowed;
   return out;
 }

@@ -114,7 +114,7 @@ __device__ inline WideOutcome wide_nucleus(RowCtx &c, float max_logit, float min
       }
     }
   }
-  c.cluster.sync();  // every CTA's histogram is complete; nobody touches it again before the verdict exchange below
+  c.cluster.sync();  // every CTA's histogram is complete; nobody touches it again before the outcome exchange below
   // Every CTA totals its own segment of the bins over all CTAs' histograms (remote shared-memory loads), brackets
   // the masses, and takes prefix sums inside the segment; the segment totals then go round the cluster, which gives
   // every CTA the total bracket and its segment's offset, and a second round agrees on the window.
@@ -152,10 +152,10 @@ __device__ inline WideOutcome wide_nucleus(RowCtx &c, float max_logit, float min
   double lo0, hi0;
   int cn0, crowd;
   block_prefix2x3(c, lo, hi, cnt, crowded ? 1 : 0, &lo0, &hi0, &cn0, &crowd);
-  if (c.tid == kThreads - 1) { s->verdict.d[0] = lo0 + lo[1]; s->verdict.d[1] = hi0 + hi[1]; s->verdict.i[0] = cn0 + cnt[1]; }
+  if (c.tid == kThreads - 1) { s->outcome.d[0] = lo0 + lo[1]; s->outcome.d[1] = hi0 + hi[1]; s->outcome.i[0] = cn0 + cnt[1]; }
   __syncthreads();
   Slot totals{};
-  totals.d[0] = s->verdict.d[0]; totals.d[1] = s->verdict.d[1]; totals.i[1] = s->verdict.i[0]; totals.i[0] = crowd;
+  totals.d[0] = s->outcome.d[0]; totals.d[1] = s->outcome.d[1]; totals.i[1] = s->outcome.i[0]; totals.i[0] = crowd;
   if (c.tid == 0) { s->bcast_i[0] = 0x7fffffff; s->bcast_i[1] = 0x7fffffff; }
   const Slot *all1 = exchange(c, totals);
   double base_lo = 0, base_hi = 0, z_lo = 0, z_hi = 0;
@@ -174,11 +174,11 @@ __device__ inline WideOutcome wide_nucleus(RowCtx &c, float max_logit, float min
   }
   __syncthreads();
   const int my_w0 = s->bcast_i[0], my_w1 = s->bcast_i[1];
-  if (active && (my_w0 == b0 || my_w0 == b0 + 1)) s->verdict.i[2] = my_w0 == b0 ? C0 - cnt[0] : C0;  // ids before
-  if (active && (my_w1 == b0 || my_w1 == b0 + 1)) s->verdict.i[3] = my_w1 == b0 ? C0 : C1;            // ids through
+  if (active && (my_w0 == b0 || my_w0 == b0 + 1)) s->outcome.i[2] = my_w0 == b0 ? C0 - cnt[0] : C0;  // ids before
+  if (active && (my_w1 == b0 || my_w1 == b0 + 1)) s->outcome.i[3] = my_w1 == b0 ? C0 : C1;            // ids through
   __syncthreads();
   Slot cand{};
-  cand.i[0] = my_w0; cand.i[1] = my_w1; cand.i[2] = s->verdict.i[2]; cand.i[3] = s->verdict.i[3];
+  cand.i[0] = my_w0; cand.i[1] = my_w1; cand.i[2] = s->outcome.i[2]; cand.i[3] = s->outcome.i[3];
   __syncthreads();
   const Slot *all2 = exchange(c, cand);
   int w0 = 0x7fffffff, w1 = 0x7fffffff, before_w0 = 0, through = 0;
@@ -187,7 +187,7 @@ __device__ inline WideOutcome wide_nucleus(RowCtx &c, float max_logit, float min
     if (all2[r].i[1] != 0x7fffffff) { w1 = all2[r].i[1]; through = all2[r].i[3]; }
   }
   // not this path's case: no window, a nucleus that certainly fits the candidate list (the small-support path's
-  // case), a window larger than the list, or a wrapped mass -- the same verdict in every CTA
+  // case), a window larger than the list, or a wrapped mass -- the same outcome in every CTA
   if (w0 == 0x7fffffff || w1 == 0x7fffffff || w1 < w0 || through <= kListCap / 2 || through - before_w0 > kListCap || any_crowd)
     return out;
 
@@ -197,7 +197,7 @@ __device__ inline WideOutcome wide_nucleus(RowCtx &c, float max_logit, float min
   double z_lane = 0, def_lane = 0;
   int def_count = 0, n_band = 0;  // n_band is warp-uniform
   const float edge0 = float(w0), edge1 = w1 >= kWideBins - 1 ? CUDART_INF_F : float(w1 + 1);
-  // (the mass histogram shares its memory with the lists: rank 0 pulled it before the verdict exchange above)
+  // (the mass histogram shares its memory with the lists: rank 0 pulled it before the outcome exchange above)
   for (int it = 0; it < c.region; it += 32) {
     const int j = c.warp * c.region + it + c.lane;
     bool inside = false;
@@ -326,17 +326,17 @@ __device__ inline WideOutcome wide_nucleus(RowCtx &c, float max_logit, float min
     if (c.tid == 0) {
       s->list_count = 0;
       // mass_before >= lo: the crossing is (or may be) before the window; pos unset: not reached inside it
-      s->verdict.i[0] = (mass_before < lo && pos != 0x7fffffff) ? 1 : 0;
+      s->outcome.i[0] = (mass_before < lo && pos != 0x7fffffff) ? 1 : 0;
     }
     if (pos != 0x7fffffff && (pos >> 1) == c.tid) {
       const int i = pos & 1;
       const double mass_at = i ? through1 : through0, prev_at = mass_at - e[i];
-      s->verdict.i[1] = ((mass_at < hi) || (prev_at >= lo)) ? 1 : 0;
-      s->verdict.f[0] = ys[i]; s->verdict.i[2] = int(uint32_t(keys[pos]));
-      s->verdict.i[3] = n_before + pos + 1; s->verdict.d[0] = mass_at;
+      s->outcome.i[1] = ((mass_at < hi) || (prev_at >= lo)) ? 1 : 0;
+      s->outcome.f[0] = ys[i]; s->outcome.i[2] = int(uint32_t(keys[pos]));
+      s->outcome.i[3] = n_before + pos + 1; s->outcome.d[0] = mass_at;
     }
     __syncthreads();
-    v = s->verdict;
+    v = s->outcome;
     __syncthreads();
   }
   v = exchange(c, v)[0];

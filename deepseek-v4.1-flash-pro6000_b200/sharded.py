@@ -314,7 +314,7 @@ class RowExchange:
                                                                             C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int,
                                                                             C.c_int64, C.c_void_p, C.c_void_p]
         self._lib = lib
-        # Every rank must end up with the same verdict (a rank that raised alone would leave the others waiting in the
+        # Every rank must end up with the same answer (a rank that raised alone would leave the others waiting in the
         # next collective): failures are recorded, agreed on with one all-reduce, and only then raised everywhere.
         failure = None
         handle = C.create_string_buffer(64)
@@ -350,9 +350,9 @@ class RowExchange:
             self._opened.append(p)
             ptrs.append(p.value)
         if self.world > 1:
-            verdict = torch.tensor([0 if failure else 1], dtype=torch.int32, device=device)
-            dist.all_reduce(verdict, op=dist.ReduceOp.MIN, group=group)
-            if verdict.item() == 0:
+            agreed = torch.tensor([0 if failure else 1], dtype=torch.int32, device=device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
+            if agreed.item() == 0:
                 failure = failure or "another rank could not map the peer buffers"
         if failure:
             self.full = None

@@ -144,7 +144,7 @@ def test_same_tokens_as_cluster_kernel_at_1024_rows(pkg):
 
 def test_batch_weight_error_bound(pkg):
     """The FP64 pass's weight 2^-((max - y) * log2(e) / T) (64-entry table of 2^(-j/64) times a Taylor polynomial of
-    degree 4) against long double: within the 1024 * 2^-53 relative that the resolve kernel's bounds budget, over
+    degree 4) against long double: within the 1024 * 2^-53 relative that the resolve kernel's bounds allow for, over
     temperatures, offsets and ranges up to the path's exponent limit; exactly 1 at the maximum."""
     lib = pkg.lib()
     lib.ds41_b200_test_batch_weight.argtypes = [C.c_void_p, C.c_float, C.c_double, C.c_void_p, C.c_int, C.c_void_p]
