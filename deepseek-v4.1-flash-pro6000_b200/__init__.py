@@ -381,6 +381,86 @@ def score_logits(logits, top_n=0):
     return lse, top1, ids, lp, status
 
 
+class ProbArgs(C.Structure):
+    _fields_ = [("struct_bytes", C.c_uint32), ("rows", C.c_int32), ("vocab", C.c_int32), ("logits", C.c_void_p),
+                ("logits_stride", C.c_int64), ("temperature", C.c_double), ("top_p", C.c_double),
+                ("probabilities", C.c_void_p), ("status", C.c_void_p), ("scratch", C.c_void_p),
+                ("scratch_bytes", C.c_size_t)]
+
+
+def probabilities(logits, temperature, top_p):
+    """The reference's probability rows on the device (ds41_spark_probabilities through the adapter's temperature
+    floor: engine/third_party/spark/src/sampling.cpp:30-38, engine/src/sampling.cpp:205-219).  Returns (float64
+    [rows, vocab], int32 status [rows]); a row with non-finite logits is NaN with a negative status."""
+    logits = _dev(logits, torch.float32, "logits")
+    rows, vocab = logits.shape
+    L = lib()
+    L.ds41_b200_probabilities_scratch_bytes.restype = C.c_size_t
+    L.ds41_b200_probabilities_scratch_bytes.argtypes = [C.c_int]
+    L.ds41_b200_probabilities.argtypes = [C.POINTER(ProbArgs), _P]
+    need = L.ds41_b200_probabilities_scratch_bytes(rows)
+    out = torch.empty((rows, vocab), dtype=torch.float64, device=logits.device)
+    status = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    scratch = torch.empty(need, dtype=torch.uint8, device=logits.device)
+    a = ProbArgs(C.sizeof(ProbArgs), rows, vocab, logits.data_ptr(), logits.stride(0), float(temperature), float(top_p),
+                 out.data_ptr(), status.data_ptr(), scratch.data_ptr(), need)
+    with torch.cuda.device(logits.device):
+        _check(L.ds41_b200_probabilities(C.byref(a), _stream()), "ds41_b200_probabilities")
+    return out, status
+
+
+def sample_probabilities(p, seeds, steps, slot=0, purpose=Purpose.Target):
+    """ds41_spark_sample_v2 on device rows (sampling.cpp:12-21,59): validate, then the sequential inverse CDF.  p float64
+    [rows, vocab]; returns (tokens, status)."""
+    p = _dev(p, torch.float64, "p")
+    rows, vocab = p.shape
+    seeds, steps = _dev(seeds, torch.int64, "seeds"), _dev(steps, torch.int64, "steps")
+    tokens = torch.empty(rows, dtype=torch.int32, device=p.device)
+    status = torch.empty(rows, dtype=torch.int32, device=p.device)
+    L = lib()
+    L.ds41_b200_sample_probabilities.argtypes = [_P, C.c_int, C.c_int, _i64, _P, _P, C.c_uint32, C.c_uint32, _P, _P, _P]
+    with torch.cuda.device(p.device):
+        _check(L.ds41_b200_sample_probabilities(p.data_ptr(), rows, vocab, p.stride(0), seeds.data_ptr(), steps.data_ptr(),
+                                                int(slot), int(purpose), tokens.data_ptr(), status.data_ptr(), _stream()),
+               "ds41_b200_sample_probabilities")
+    return tokens, status
+
+
+def verify_probabilities(draft_ids, q, p, drafts, seeds, steps, greedy=False):
+    """ds41_spark_verify_v2 on device rows (sampling.cpp:39-56).  p float64 [sequences * (drafts + 1), vocab], q float64
+    [sequences * drafts, vocab] (None when greedy), draft_ids int32 [sequences * drafts].  Returns (results, status)."""
+    p = _dev(p, torch.float64, "p")
+    vocab = p.shape[1]
+    sequences = p.shape[0] // (drafts + 1)
+    q = _dev(q, torch.float64, "q") if q is not None else None
+    draft_ids = _dev(draft_ids, torch.int32, "draft_ids") if drafts else None
+    seeds, steps = _dev(seeds, torch.int64, "seeds"), _dev(steps, torch.int64, "steps")
+    results = torch.empty(sequences * C.sizeof(SparkResult), dtype=torch.uint8, device=p.device)
+    status = torch.empty(sequences, dtype=torch.int32, device=p.device)
+    L = lib()
+    L.ds41_b200_verify_probabilities.argtypes = [_P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P, _P, _P, _P]
+    with torch.cuda.device(p.device):
+        _check(L.ds41_b200_verify_probabilities(draft_ids.data_ptr() if draft_ids is not None else None,
+                                                q.data_ptr() if q is not None else None, p.data_ptr(), sequences,
+                                                drafts, vocab, 1 if greedy else 0, seeds.data_ptr(), steps.data_ptr(),
+                                                results.data_ptr(), status.data_ptr(), _stream()),
+               "ds41_b200_verify_probabilities")
+    return results, status
+
+
+def spark_sample_gpu_v2(p_f32, seed, step, slot=0, purpose=Purpose.Target):
+    """The reference's GPU sampler entry point (spark.h:133; sampling.cu:24-39,71): one FP32 measure row on the device,
+    normalised in FP64.  Returns the token (−1: in-band failure)."""
+    p_f32 = _dev(p_f32, torch.float32, "p")
+    token = torch.empty(1, dtype=torch.int32, device=p_f32.device)
+    L = lib()
+    L.ds41_spark_sample_gpu_v2.argtypes = [_P, C.c_int, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, _P, _P]
+    with torch.cuda.device(p_f32.device):
+        _check(L.ds41_spark_sample_gpu_v2(p_f32.data_ptr(), p_f32.numel(), int(seed), int(step), int(slot), int(purpose),
+                                          token.data_ptr(), _stream()), "ds41_spark_sample_gpu_v2")
+    return int(token.item())
+
+
 SAMPLER_PHASES = ("flat_stats_kernel", "flat_hist_kernel", "flat_window_kernel", "flat_mass_kernel",
                   "flat_resolve_kernel", "row_kernel", "replay_sample_kernel")
 
