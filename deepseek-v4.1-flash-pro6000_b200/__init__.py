@@ -313,6 +313,21 @@ def head_bf16(x, w_bf16, out=None, decode_symbol=False):
     return out
 
 
+def head_f32(x, w_f32, out=None):
+    """FP32 head (the reference's default target head, ds41_dense_cublas(f32=1): dense/src/ops.cu:120-128): x fp32
+    [M, K], w fp32 [N, K] -> fp32 [M, N]."""
+    x, w_f32 = _dev(x, torch.float32, "x"), _dev(w_f32, torch.float32, "w")
+    M, K = x.shape
+    N = w_f32.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    L = lib()
+    L.ds41_b200_head_f32.argtypes = [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P]
+    with torch.cuda.device(x.device):
+        _check(L.ds41_b200_head_f32(x.data_ptr(), w_f32.data_ptr(), out.data_ptr(), M, N, K, _stream()), "ds41_b200_head_f32")
+    return out
+
+
 def head_compact(x, w_bf16, out=None):
     """The drafter's BF16 head (ds41_dense_head_compact, components/dense/src/compact.cu:10-24,44-50): x fp32 [M,K]
     (M <= 8), weights bf16 [N,K] -> fp32 [M,N], bit-identical to the reference kernel."""

@@ -93,6 +93,13 @@ int ds41_fuse_head_decode(const float *x, const void *weights_bf16, float *out, 
 int ds41_b200_head_bf16(const float *x, const void *weights_bf16, float *out, int M, int N, int K,
                         cudaStream_t stream);
 
+/* FP32 head: y[m, n] = sum_k w[n, k] * x[m, k] with FP32 weights [N, K] (K contiguous), x [M, K], y [M, N], M <= 8, K a
+ * multiple of 128, M * K * 4 <= 224 KB.  Stands in for the reference's default target head, ds41_dense_cublas(f32 = 1)
+ * on FP32-promoted weights (components/dense/src/ops.cu:120-128; engine/src/forward.cu:1306-1318).  cuBLAS does not
+ * specify its order of summation, so there is nothing to match bit for bit: the order here is fixed (stated in
+ * csrc/head_f32.cu) and the result is within the FP32 bound of the exact product. */
+int ds41_b200_head_f32(const float *x, const float *w, float *y, int M, int N, int K, cudaStream_t stream);
+
 /* Drafter head: the reference's own symbol and argument check (components/dense/include/ds41/dense.h;
  * src/compact.cu:10-24,44-50: 1 <= M <= 8, K a multiple of 256), x fp32 [M,K], weights bf16 [N,K], y fp32 [M,N].  The
  * reference kernel's FP32 order is kept (four fused-multiply-add chains per lane over 8-wide loads,
