@@ -185,7 +185,9 @@ __global__ void final_norm_kernel(const __nv_bfloat16 *__restrict__ h, const flo
 
 template <int M>
 cudaError_t launch_compact(const float *x, const void *w, float *y, int N, int K, cudaStream_t stream) {
-  constexpr int kRowsPerWarp = M <= 6 ? 4 : 2;  // weight rows that share one read of an activation fragment
+  // weight rows that share one read of an activation fragment; at one or two batch rows the kernel only streams
+  // weights and more resident CTAs (fewer registers each) keep more loads in flight
+  constexpr int kRowsPerWarp = M <= 2 ? 2 : M <= 6 ? 4 : 2;
   const size_t smem = size_t(M) * K * sizeof(float);
   static thread_local int configured = -1;
   int dev = 0, sms = 0;
@@ -197,7 +199,7 @@ cudaError_t launch_compact(const float *x, const void *w, float *y, int N, int K
     if (e != cudaSuccess) return e;
     configured = dev;
   }
-  const int per_sm = smem <= 100 * 1024 ? 2 : 1;
+  const int per_sm = smem <= 48 * 1024 ? 4 : smem <= 100 * 1024 ? 2 : 1;
   const int groups = (N + kRowsPerWarp - 1) / kRowsPerWarp;
   int grid = sms * per_sm;
   if (grid > (groups + kHeadWarps - 1) / kHeadWarps) grid = (groups + kHeadWarps - 1) / kHeadWarps;
