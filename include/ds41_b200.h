@@ -158,8 +158,11 @@ typedef struct ds41_b200_sample_args {
                                  per row, by two batch-parallel paths before the cluster kernel: without top_k (rows
                                  16-byte aligned, vocab >= 16384) the batch path (grid-wide kernels: histogram,
                                  window, FP64 masses, resolve), then the streaming path for small nuclei (chunk
-                                 records + a per-row combine).  Rows neither can certify, and calls without scratch,
-                                 use the cluster kernel.  Same results on every path. */
+                                 records + a per-row combine).  Rows neither can take, and calls without scratch,
+                                 use the cluster kernel.  Same results on every path.  With scratch, rows whose
+                                 decision fell inside the rounding bound of the parallel sums (status bits 1 / 2) are
+                                 redone in the same call in the reference's order of operations and leave with
+                                 status 0 (the scratch holds the replay's rows too: about 10 MB). */
   size_t scratch_bytes;
   const void *row_extremes;   /* optional: the [rows] records ds41_b200_head_fp8_stats wrote for these logits (16 bytes
                                  each); the batch path then skips its own maximum / minimum pass.  NULL otherwise. */
@@ -175,7 +178,10 @@ int ds41_b200_sample_logits(const ds41_b200_sample_args *args, cudaStream_t stre
  * from (spark.h:101-105).  Sequence s uses the address (seeds[s], steps[s], slot = position, purpose =
  * ACCEPT / RESIDUAL / TARGET) exactly as the reference.  temperature 0 selects the greedy rule (draft_logits
  * may then be NULL).  `scratch` is caller-owned device memory of ds41_b200_verify_scratch_bytes() bytes (16-byte
- * aligned); with at least 48 bytes per logits row the slower cluster-only path is used instead of the streaming one. */
+ * aligned): 48 bytes of statistics per logits row, the streaming path's chunk records, and 7.3 MB for the replay of
+ * transactions whose decisions fell inside the rounding bound (status bits 1 / 2 / 4 / 8: redone in the same call in
+ * the reference's order, they leave with status 0).  With less the call still works: without the replay's share the
+ * bits stay in the status words; with the statistics alone every row goes through the cluster kernel. */
 typedef struct ds41_b200_verify_args {
   uint32_t struct_bytes;
   int32_t sequences, drafts, vocab;
