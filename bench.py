@@ -14,6 +14,11 @@ selected with --workload.
 Prints ONE JSON line (rank 0).  Weights stay resident in HBM (as in the reference engine); `value` is measured with the
 step's inputs already on the device, `e2e` with the hidden states copied from pinned host memory and the token ids
 read back every step.  `--impl reference` times the reference's own CPU sampling rule on the host cores.
+Timing: a step is one CUDA-graph replay (at every N: the sharded step is captured with its collectives).  K steps are
+timed between two CUDA events (max over ranks); that block is repeated until about a second has been timed and the
+median block is reported, with the minimum and maximum beside it (`timing`).  The head and the sampler call are also
+timed on their own (`roofline`, `other_kernels`), the sampler call's kernels one by one through the library's phase
+events.  With several GPUs the rows exchange runs in teams of `--vocab-ranks` ranks (default two from 4 GPUs on).
 """
 import argparse
 import math
@@ -844,7 +849,8 @@ def main():
                 total = sum(phases.values()) or 1.0
                 top = max(phases, key=phases.get)
                 entry_["kernels"] = {k: {"ms": v, "share": v / total,
-                                         "traffic": (NCU_TRAFFIC_PER_ROW.get(k) or 0) * rows_here or None}
+                                         "traffic": (NCU_TRAFFIC_PER_ROW.get(k) or 0) * rows_here or None,
+                                         "traffic_extrapolated": k in EXTRAPOLATED_TRAFFIC}
                                      for k, v in phases.items()}
                 entry_["dominant_kernel"] = top
                 entry_["traffic"] = sampler_traffic(phases, rows_here)
