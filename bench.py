@@ -849,7 +849,7 @@ def main():
                 total = sum(phases.values()) or 1.0
                 top = max(phases, key=phases.get)
                 entry_["kernels"] = {k: {"ms": v, "share": v / total,
-                                         "traffic": (NCU_TRAFFIC_PER_ROW.get(k) or 0) * rows_here or None,
+                                         "traffic": ((NCU_TRAFFIC_PER_ROW.get(k) or 0) * rows_here or None) if v > 0.004 else None,
                                          "traffic_extrapolated": k in EXTRAPOLATED_TRAFFIC}
                                      for k, v in phases.items()}
                 entry_["dominant_kernel"] = top
